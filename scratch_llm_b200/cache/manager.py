@@ -41,7 +41,7 @@ class Group:
     spec: KVSpec
     entries: list[int]
     pool: PagePool
-    pages: torch.Tensor | None = None  # [n_entries, n_pages, 2, kv_heads, page_size, head_dim]
+    pages: torch.Tensor | None = None  # [n_entries, n_pages, planes, kv_heads, page_size, head_dim]
 
 
 @dataclass
@@ -89,7 +89,7 @@ class CacheManager:
         if self.device is not None:
             for group in self.groups:
                 s = group.spec
-                group.pages = torch.empty((len(group.entries), n_pages, 2, s.n_kv_heads,
+                group.pages = torch.empty((len(group.entries), n_pages, s.planes, s.n_kv_heads,
                                            page_size, s.head_dim), dtype=dtype,
                                           device=self.device)
                 if poison_free_pages:

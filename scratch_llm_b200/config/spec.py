@@ -58,11 +58,22 @@ class Run:
     """One entry of the run order: run ``layer`` against cache entry ``cache``.
 
     ``write`` False means the mixer reads the cache entry another run filled earlier in the
-    same step and stores nothing itself."""
+    same step and stores nothing itself.  ``join`` (an index into ``ModelSpec.joins``): right
+    before this run the stream is joined with the embedding output by that part."""
 
     layer: int
     cache: int
     write: bool = True
+    join: int | None = None
+
+
+@dataclass(frozen=True)
+class JoinSpec:
+    """A join of the stream with the embedding output (a key of STREAM_JOINS with its sizes)
+    and the tensor-name prefix of its weights."""
+
+    part: PartSpec
+    prefix: str
 
 
 @dataclass(frozen=True)
@@ -86,6 +97,8 @@ class ModelSpec:
     #: not 0: a sinusoidal position vector is added to the embedded tokens, entry 2i gets
     #: ``sin(p * base^(-2i / hidden_size))`` and entry 2i + 1 the cosine of the same angle
     position_sinusoid_base: float = 0.0
+    #: joins of the stream with the embedding output, which runs name by index (``Run.join``)
+    joins: tuple[JoinSpec, ...] = ()
 
     def __post_init__(self) -> None:
         if self.position_sinusoid_base < 0:
@@ -97,6 +110,9 @@ class ModelSpec:
             if not 0 <= run.layer < len(self.layers):
                 raise ValueError(f"run order names layer {run.layer}, but there are "
                                  f"{len(self.layers)} layers")
+            if run.join is not None and not 0 <= run.join < len(self.joins):
+                raise ValueError(f"run order names join {run.join}, but there are "
+                                 f"{len(self.joins)} joins")
             if run.write:
                 if run.cache in seen_write:
                     raise ValueError(f"cache entry {run.cache} is written by two runs")

@@ -115,6 +115,9 @@ struct AttnArgs {
     // this index is not written (and *part_error is set, if given) instead of landing outside
     int64_t part_tokens; int* part_error;
     int H; int G; float scale_log2; int window;
+    // 2: a page holds keys, then values; 1: one vector per token, its key and (by its leading
+    // entries) its value
+    int planes;
     // slopes (may be null): float [H]; slopes[h] * (query position - key position) is taken off
     // the scaled score of head h.  sinks (may be null): float [H]; exp(sinks[h]) joins the
     // softmax's denominator of head h, once, with no value behind it (with several splits it is
@@ -188,7 +191,7 @@ __global__ void __launch_bounds__(THREADS, SPLIT ? 3 : 2) attn_mma_kernel(const 
     }
     cp_async_commit();
 
-    const int64_t v_off = (int64_t)a.G * a.page_size * HD;
+    const int64_t v_off = (int64_t)(a.planes - 1) * a.G * a.page_size * HD;
     // Where a tile's keys live: thread j < 64 looks up key j's page once and leaves the element
     // offset of its K row in shared memory (-1: no such key); all threads then copy 16-byte
     // pieces from those offsets.  The lookup for a tile happens one step before its copy.
@@ -200,7 +203,7 @@ __global__ void __launch_bounds__(THREADS, SPLIT ? 3 : 2) attn_mma_kernel(const 
             if (tile < tile_end && kpos <= last_pos) {
                 const int page = a.block_table[(int64_t)r * a.table_stride + kpos / a.page_size];
                 if (page >= 0)
-                    off = (((long long)page * 2 * a.G + g) * a.page_size + kpos % a.page_size) * HD;
+                    off = (((long long)page * a.planes * a.G + g) * a.page_size + kpos % a.page_size) * HD;
             }
             key_off[slot][tid] = off;
         }
@@ -524,7 +527,7 @@ __global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnAr
     }
     cp_async_commit();
 
-    const int64_t v_off = (int64_t)a.G * a.page_size * HD;
+    const int64_t v_off = (int64_t)(a.planes - 1) * a.G * a.page_size * HD;
     // With the rotation fused (rows of one new token at position pos0): everything it needs
     // from global memory is requested now, so that it has arrived when the tiles have.
     // Thread t rotates pair t % (HD / 2) of the query heads t / (HD / 2), ... and of the new key,
@@ -593,7 +596,7 @@ __global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnAr
             if (tile < tile_end && kpos <= last_pos) {
                 const int page = a.block_table[(int64_t)r * a.table_stride + kpos / a.page_size];
                 if (page >= 0)
-                    off = (((long long)page * 2 * a.G + g) * a.page_size + kpos % a.page_size) * HD;
+                    off = (((long long)page * a.planes * a.G + g) * a.page_size + kpos % a.page_size) * HD;
             }
             key_off[slot][tid] = off;
         }
@@ -690,7 +693,7 @@ __global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnAr
             bf16* v_row = Vs + stage * BKV * LDS + in_tile * LDS;
             const int page = a.block_table[(int64_t)r * a.table_stride + pos0 / a.page_size];
             bf16* k_dst = const_cast<bf16*>(a.pages) +
-                          (((long long)page * 2 * a.G + g) * a.page_size + pos0 % a.page_size) * HD;
+                          (((long long)page * a.planes * a.G + g) * a.page_size + pos0 % a.page_size) * HD;
             bf16* v_dst = k_dst + v_off;
 #pragma unroll
             for (int u = 0; u < K_PER; ++u) {
@@ -1017,7 +1020,8 @@ SLLM_EXPORT int64_t sllm_attn_mma_scratch_floats(int64_t n_tokens, int H, int n_
 }
 
 // q / out: [n_tokens, stride] bfloat16 with head h at columns [h*HD, (h+1)*HD).
-// pages: [n_pages, 2, G, page_size, HD] bfloat16.  block_table: [rows, table_stride], -1 = none.
+// pages: [n_pages, planes, G, page_size, HD] bfloat16 (planes = 2: keys, then values; 1: one
+// vector per token that is key and value).  block_table: [rows, table_stride], -1 = none.
 // row_list: the n_list rows this launch serves (nullptr: rows 0..n_list-1).
 // split = 0: the wide kernel; max_new = the largest number of new tokens of a listed row.
 // split = 1: the split kernel with n_splits CTAs along the keys; for n_splits > 1,
@@ -1030,8 +1034,9 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
                               float scale, int window, int split, int n_splits, float* scratch,
                               int64_t n_tokens_total, const float* slopes, const float* sinks,
                               const void* gate, int64_t gate_stride, int* merge_count,
-                              cudaStream_t stream) {
+                              int planes, cudaStream_t stream) {
     if (n_list <= 0 || max_new <= 0) return 0;
+    if (planes < 1 || planes > 2) return (int)cudaErrorInvalidValue;
     if (H <= 0 || G <= 0 || H % G != 0 || page_size <= 0 || window < 0 || n_list > 65535 ||
         G > 65535 || (q_stride % 8) != 0 || (out_stride % 2) != 0)
         return (int)cudaErrorInvalidValue;
@@ -1048,6 +1053,7 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
     a.slopes = slopes; a.sinks = sinks;
     a.gate = (const bf16*)gate; a.gate_stride = gate_stride;
     a.cos_t = nullptr; a.sin_t = nullptr; a.interleaved = 1; a.write_kv = 0;
+    a.planes = planes;
     a.H = H; a.G = G; a.scale_log2 = scale * 1.4426950408889634f; a.window = window;
     const int GS = H / G;
     cudaError_t e;
@@ -1137,6 +1143,7 @@ SLLM_EXPORT int sllm_attn_mma_decode_biased(const void* qkv, int64_t qkv_stride,
     a.part_o = nullptr; a.part_lse = nullptr; a.n_splits = n_splits;
     a.part_tokens = n_tokens_total; a.part_error = nullptr;
     a.merge_count = n_splits > 1 ? merge_count : nullptr;
+    a.planes = 2;
     a.H = H; a.G = G; a.scale_log2 = scale * 1.4426950408889634f; a.window = window;
     a.cos_t = cos_t; a.sin_t = sin_t; a.interleaved = interleaved; a.write_kv = write_kv;
     a.rope_bias = bias; a.rot = rot;
@@ -1270,6 +1277,7 @@ SLLM_EXPORT int sllm_attn_mma_split_noalloc(const void* q, int64_t q_stride, con
     a.n_splits = n_splits;
     a.part_tokens = n_tokens_total; a.part_error = g_noalloc_flag_ptr[dev];
     a.cos_t = nullptr; a.sin_t = nullptr; a.interleaved = 1; a.write_kv = 0;
+    a.planes = 2;
     a.H = H; a.G = G; a.scale_log2 = scale * 1.4426950408889634f; a.window = window;
     const int GS = H / G;
     const size_t smem = smem_bytes<true>();

@@ -11,7 +11,7 @@
 //
 // Keys are consumed in tiles of 32 that are aligned to absolute positions, in ascending
 // order, so a query's result does not depend on how its prompt was cut or on its neighbours.
-// Compiled once per head size: -DSLLM_HEAD_DIM=<1 to 512>.
+// Compiled once per head size: -DSLLM_HEAD_DIM=<1 to 640>.
 #include "common.cuh"
 
 #ifndef SLLM_HEAD_DIM
@@ -21,7 +21,7 @@
 namespace sllm {
 
 constexpr int HD = SLLM_HEAD_DIM;
-static_assert(HD >= 1 && HD <= 512, "head size: 1 to 512");
+static_assert(HD >= 1 && HD <= 640, "head size: 1 to 640");
 constexpr int BQ = 16, BKV = 32, THREADS = 128, ROWS_PER_WARP = 4;
 constexpr int DPL = (HD + 31) / 32;  // head dims per lane
 constexpr int KS_LD = HD + 1;
@@ -36,7 +36,7 @@ attn_simt_kernel(const T* __restrict__ q, int64_t q_stride, const T* __restrict_
                  const int* __restrict__ block_table, int table_stride, int page_size,
                  const int* __restrict__ row_start, const int* __restrict__ row_pos0,
                  T* __restrict__ out, int64_t out_stride, int H, int G, float scale, int window,
-                 const float* __restrict__ slopes, const float* __restrict__ sinks) {
+                 const float* __restrict__ slopes, const float* __restrict__ sinks, int planes) {
     extern __shared__ float smem[];
     __shared__ long long key_base[BKV];  // element offset of each key's K row, -1 if absent
     float* Qs = smem;
@@ -73,7 +73,8 @@ attn_simt_kernel(const T* __restrict__ q, int64_t q_stride, const T* __restrict_
 #pragma unroll
         for (int c = 0; c < DPL; ++c) acc[a][c] = 0.f;
     }
-    const int64_t v_offset = (int64_t)G * page_size * HD;
+    // (one plane: the values are the leading entries of the keys themselves)
+    const int64_t v_offset = (int64_t)(planes - 1) * G * page_size * HD;
 
     for (int kt = k_lo; kt <= last_pos; kt += BKV) {
         __syncthreads();  // the previous tile's Ks / Vs / key_base are no longer read
@@ -83,7 +84,7 @@ attn_simt_kernel(const T* __restrict__ q, int64_t q_stride, const T* __restrict_
             if (kpos <= last_pos) {
                 const int page = block_table[(int64_t)r * table_stride + kpos / page_size];
                 if (page >= 0)
-                    base = (((long long)page * 2 * G + g) * page_size + kpos % page_size) * HD;
+                    base = (((long long)page * planes * G + g) * page_size + kpos % page_size) * HD;
             }
             key_base[tid] = base;
         }
@@ -168,7 +169,8 @@ using namespace sllm;
 SLLM_EXPORT int sllm_attn_simt_head_dim() { return HD; }
 
 // q: [n_tokens, q_stride] with head h at columns [h*HD, (h+1)*HD); out likewise.
-// pages: [n_pages, 2, G, page_size, HD].  block_table: [n_rows, table_stride], -1 = no page.
+// pages: [n_pages, planes, G, page_size, HD]; planes = 2: keys, then values; planes = 1: one
+// vector per token that is its key and, by its leading entries, its value.  block_table: [n_rows, table_stride], -1 = no page.
 // row_start: [n_rows + 1] token offsets; row_pos0: [n_rows] position of each row's first token.
 // max_new: the largest number of new tokens of any row.  window: 0 = all keys.
 // slopes (may be null): float [H]; slopes[h] * (query position - key position) is taken off the
@@ -179,9 +181,9 @@ SLLM_EXPORT int sllm_attn_simt(const void* q, int64_t q_stride, const void* page
                                const int* row_start, const int* row_pos0, void* out,
                                int64_t out_stride, int n_rows, int max_new, int H, int G,
                                float scale, int window, const float* slopes, const float* sinks,
-                               int dtype, cudaStream_t stream) {
+                               int planes, int dtype, cudaStream_t stream) {
     if (n_rows <= 0 || max_new <= 0) return 0;
-    if (H <= 0 || G <= 0 || H % G != 0 || page_size <= 0 || window < 0)
+    if (H <= 0 || G <= 0 || H % G != 0 || page_size <= 0 || window < 0 || planes < 1 || planes > 2)
         return (int)cudaErrorInvalidValue;
     if (n_rows > 65535 || H > 65535) return (int)cudaErrorInvalidValue;
     const size_t smem = smem_floats() * sizeof(float);
@@ -193,7 +195,8 @@ SLLM_EXPORT int sllm_attn_simt(const void* q, int64_t q_stride, const void* page
         if (e != cudaSuccess) return (int)e;
         attn_simt_kernel<float><<<grid, THREADS, smem, stream>>>(
             (const float*)q, q_stride, (const float*)pages, block_table, table_stride, page_size,
-            row_start, row_pos0, (float*)out, out_stride, H, G, scale, window, slopes, sinks);
+            row_start, row_pos0, (float*)out, out_stride, H, G, scale, window, slopes, sinks,
+            planes);
     } else if (dtype == 1) {
         e = cudaFuncSetAttribute(attn_simt_kernel<__nv_bfloat16>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -201,7 +204,7 @@ SLLM_EXPORT int sllm_attn_simt(const void* q, int64_t q_stride, const void* page
         attn_simt_kernel<__nv_bfloat16><<<grid, THREADS, smem, stream>>>(
             (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, block_table,
             table_stride, page_size, row_start, row_pos0, (__nv_bfloat16*)out, out_stride, H, G,
-            scale, window, slopes, sinks);
+            scale, window, slopes, sinks, planes);
     } else {
         return (int)cudaErrorInvalidValue;
     }

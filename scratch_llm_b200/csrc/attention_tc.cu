@@ -214,6 +214,8 @@ struct AtcArgs {
     // scores, exp(sinks[h]) joins its softmax denominator once.  oob_row: a row beyond the cache
     // tensor: a copy from there brings zeros (pages the row has given back, or never held).
     int window; const float* slopes; const float* sinks; int oob_row;
+    // 2: a page holds keys, then values; 1: one vector per token, its key and its value
+    int planes;
 };
 
 // BIASED: with a window, slopes and sinks (see AtcArgs); false: plain causal attention, the code
@@ -296,7 +298,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 atc_tma_3d(q_s + c * SUB_BYTES, &map_q, q_full, c * 64, g * GS, t0 + tok_first);
         }
         const int pages_per_tile = TKV / a.page_size;
-        const int64_t rows_per_page = (int64_t)2 * a.G * a.page_size;
+        const int64_t rows_per_page = (int64_t)a.planes * a.G * a.page_size;
         const int* table = a.block_table + (int64_t)r * a.table_stride;
         const int n_pages_held = last_pos / a.page_size + 1;
         // stands in for pages the row does not hold (masked keys); with a window the row may have
@@ -327,7 +329,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 const int i = lane + 32 * u;
                 if (i >= pages_per_tile) break;
                 int64_t row_k = (int64_t)my_page[u] * rows_per_page + (int64_t)g * a.page_size;
-                int64_t row_v = row_k + (int64_t)a.G * a.page_size;
+                int64_t row_v = row_k + (int64_t)(a.planes - 1) * a.G * a.page_size;
                 if (BIASED && my_page[u] < 0) row_k = row_v = a.oob_row;
                 for (int c = 0; c < NCB; ++c) {
                     atc_tma_2d(k_dst + c * SUB_BYTES + i * a.page_size * 128, &map_kv, &kv_full[s],
@@ -671,7 +673,7 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                                t0 + (q0 + x * TQ) / GS);
         }
         const int pages_per_tile = TKV / a.page_size;
-        const int64_t rows_per_page = (int64_t)2 * a.G * a.page_size;
+        const int64_t rows_per_page = (int64_t)a.planes * a.G * a.page_size;
         const int* table = a.block_table + (int64_t)r * a.table_stride;
         const int n_pages_held = last_pos / a.page_size + 1;
         const int spare = table[0];   // stands in for pages the row does not hold (masked keys)
@@ -699,7 +701,7 @@ attn_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                 const int i = lane + 32 * u;
                 if (i >= pages_per_tile) break;
                 const int64_t row_k = (int64_t)my_page[u] * rows_per_page + (int64_t)g * a.page_size;
-                const int64_t row_v = row_k + (int64_t)a.G * a.page_size;
+                const int64_t row_v = row_k + (int64_t)(a.planes - 1) * a.G * a.page_size;
                 for (int c = 0; c < NCB; ++c) {
                     atc_tma_2d(k_dst + c * SUB_BYTES + i * a.page_size * 128, &map_kv, &kv_full[s],
                                c * 64, (int)row_k);
@@ -996,21 +998,22 @@ SLLM_EXPORT int sllm_attn_tc_error() {
 }
 
 // q / out: [n_tokens, stride] bfloat16, head h at columns [h*HD, (h+1)*HD).  pages:
-// [n_pages, 2, G, page_size, HD] bfloat16 (places no listed row uses may hold anything).  row_list: the n_list rows served
+// [n_pages, planes, G, page_size, HD] bfloat16 (planes = 1: the values are the keys themselves; places no listed row uses may hold anything).  row_list: the n_list rows served
 // (nullptr: rows 0..n_list-1); max_new: the largest number of new tokens among them.
 static int attn_tc_launch(const void* q, int64_t q_stride, int64_t n_tokens, const void* pages,
                           int64_t n_pages, const int* block_table, int table_stride,
                           int page_size, const int* row_start, const int* row_pos0,
                           const int* row_list, int n_list, int max_new, void* out,
                           int64_t out_stride, int H, int G, float scale, bool biased, int window,
-                          const float* slopes, const float* sinks, cudaStream_t stream) {
+                          const float* slopes, const float* sinks, int planes,
+                          cudaStream_t stream) {
     if (n_list <= 0 || max_new <= 0) return 0;
     if (!sllm_attn_tc_supports(H, G, page_size, 0) || n_list > 65535 || G > 65535 ||
         (q_stride % 8) || (out_stride % 8) || ((uintptr_t)q & 15) || ((uintptr_t)pages & 15) ||
         ((uintptr_t)out & 15))
         return (int)cudaErrorInvalidValue;
     if (n_pages * 2 * G * page_size + page_size > 0x7fffffffLL || n_tokens > 0x7fffffffLL ||
-        window < 0)
+        window < 0 || planes < 1 || planes > 2)
         return (int)cudaErrorInvalidValue;
     // the query tiles of a row are the grid's z: at most 65,535 of them
     if (((int64_t)max_new * (H / G) + TQ - 1) / TQ > 65535) return (int)cudaErrorInvalidValue;
@@ -1028,8 +1031,8 @@ static int attn_tc_launch(const void* q, int64_t q_stride, int64_t n_tokens, con
                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return (int)cudaErrorInvalidValue;
     }
-    {   // the cache as rows of HD columns: row = ((page * 2 + kv) * G + g) * page_size + offset
-        cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)(n_pages * 2 * G * page_size)};
+    {   // the cache as rows of HD columns: row = ((page * planes + kv) * G + g) * page_size + offset
+        cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)(n_pages * planes * G * page_size)};
         cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
         cuuint32_t box[2] = {64u, (cuuint32_t)page_size};
         cuuint32_t elem[2] = {1u, 1u};
@@ -1044,7 +1047,8 @@ static int attn_tc_launch(const void* q, int64_t q_stride, int64_t n_tokens, con
     a.out = (bf16*)out; a.out_stride = out_stride; a.H = H; a.G = G;
     a.scale_log2 = scale * 1.4426950408889634f;
     a.window = window; a.slopes = slopes; a.sinks = sinks;
-    a.oob_row = (int)(n_pages * 2 * G * page_size);
+    a.oob_row = (int)(n_pages * planes * G * page_size);
+    a.planes = planes;
     cudaError_t e;
     if (biased) {   // one query tile per CTA: the kernel that has the window, slopes and sinks
         e = cudaFuncSetAttribute(attn_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1091,10 +1095,11 @@ SLLM_EXPORT int sllm_attn_tc(const void* q, int64_t q_stride, int64_t n_tokens, 
                              int64_t n_pages, const int* block_table, int table_stride,
                              int page_size, const int* row_start, const int* row_pos0,
                              const int* row_list, int n_list, int max_new, void* out,
-                             int64_t out_stride, int H, int G, float scale, cudaStream_t stream) {
+                             int64_t out_stride, int H, int G, float scale, int planes,
+                             cudaStream_t stream) {
     return attn_tc_launch(q, q_stride, n_tokens, pages, n_pages, block_table, table_stride,
                           page_size, row_start, row_pos0, row_list, n_list, max_new, out, out_stride,
-                          H, G, scale, false, 0, nullptr, nullptr, stream);
+                          H, G, scale, false, 0, nullptr, nullptr, planes, stream);
 }
 
 // The same with a sliding window (0: none), distance slopes and softmax sinks per head (float
@@ -1109,5 +1114,5 @@ SLLM_EXPORT int sllm_attn_tc_biased(const void* q, int64_t q_stride, int64_t n_t
                                     const float* sinks, cudaStream_t stream) {
     return attn_tc_launch(q, q_stride, n_tokens, pages, n_pages, block_table, table_stride,
                           page_size, row_start, row_pos0, row_list, n_list, max_new, out, out_stride,
-                          H, G, scale, true, window, slopes, sinks, stream);
+                          H, G, scale, true, window, slopes, sinks, 2, stream);
 }

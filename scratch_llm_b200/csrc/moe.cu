@@ -25,6 +25,10 @@ constexpr int MOE_TM = 32;   // rows of a tile
 constexpr int MOE_TN = 64;   // features of a tile
 constexpr int MOE_TK = 16;
 constexpr int MOE_MAX_TOP = 32;
+// router variants (bits of `flags`): scores are sigmoid(z) instead of a softmax over all outputs;
+// a group's score is the sum of its two largest choice scores instead of its largest; the
+// weights are the chosen scores themselves, not divided by their sum
+constexpr int MOE_SIGMOID = 1, MOE_GROUP_TOP2 = 2, MOE_RAW_WEIGHTS = 4;
 
 // One warp routes one token.  z: the token's n_total router logits; score: 2 n_total + 2 n_groups
 // floats of shared memory of this warp; counts: the experts' counters (global or shared memory).
@@ -32,34 +36,52 @@ __device__ __forceinline__ void route_token(const float* __restrict__ z,
                                             const float* __restrict__ corr, float* score,
                                             int n_total, int n_real, int n_groups, int keep,
                                             int top, int lane, int* __restrict__ ids_row,
-                                            float* __restrict__ weights_row, int* counts) {
+                                            float* __restrict__ weights_row, int* counts,
+                                            int flags) {
     float* choice = score + n_total;   // score + correction, -inf once taken or barred
-    float m = -INFINITY;
-    for (int e = lane; e < n_total; e += 32) m = fmaxf(m, z[e]);
-    m = warp_max(m);
-    float sum = 0.f;
-    for (int e = lane; e < n_total; e += 32) {
-        const float p = expf(z[e] - m);
-        score[e] = p;
-        sum += p;
-    }
-    sum = warp_sum(sum);
-    for (int e = lane; e < n_total; e += 32) {
-        const float s = score[e] / sum;
-        score[e] = s;
-        choice[e] = s + corr[e];
+    if (flags & MOE_SIGMOID) {
+        for (int e = lane; e < n_total; e += 32) {
+            const float s = 1.0f / (1.0f + expf(-z[e]));
+            score[e] = s;
+            choice[e] = s + corr[e];
+        }
+    } else {
+        float m = -INFINITY;
+        for (int e = lane; e < n_total; e += 32) m = fmaxf(m, z[e]);
+        m = warp_max(m);
+        float sum = 0.f;
+        for (int e = lane; e < n_total; e += 32) {
+            const float p = expf(z[e] - m);
+            score[e] = p;
+            sum += p;
+        }
+        sum = warp_sum(sum);
+        for (int e = lane; e < n_total; e += 32) {
+            const float s = score[e] / sum;
+            score[e] = s;
+            choice[e] = s + corr[e];
+        }
     }
     __syncwarp();
     if (n_groups > 1 && keep < n_groups) {
-        // a group's score is its largest choice score; the `keep` best groups (ties: the lower
-        // index) stay, every output of the others is barred
+        // a group's score is its largest choice score (or, with MOE_GROUP_TOP2, the sum of its
+        // two largest); the `keep` best groups (ties: the lower index) stay, every output of the
+        // others is barred
         const int per = n_total / n_groups;
         float* gscore = choice + n_total;
         float* gkept = gscore + n_groups;
         for (int g = lane; g < n_groups; g += 32) {
-            float best = -INFINITY;
-            for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, choice[e]);
-            gscore[g] = best;
+            float best = -INFINITY, second = -INFINITY;
+            for (int e = g * per; e < (g + 1) * per; ++e) {
+                const float c = choice[e];
+                if (c > best) {
+                    second = best;
+                    best = c;
+                } else if (c > second) {
+                    second = c;
+                }
+            }
+            gscore[g] = ((flags & MOE_GROUP_TOP2) && per > 1) ? best + second : best;
             gkept[g] = 0.f;
         }
         __syncwarp();
@@ -125,7 +147,7 @@ __device__ __forceinline__ void route_token(const float* __restrict__ z,
     }
     if (lane < top) {
         ids_row[lane] = my_id;
-        weights_row[lane] = my_w / (wsum + 1e-20f);
+        weights_row[lane] = (flags & MOE_RAW_WEIGHTS) ? my_w : my_w / (wsum + 1e-20f);
         if (my_id >= 0 && my_id < n_real) atomicAdd(&counts[my_id], 1);
     }
 }
@@ -135,7 +157,7 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, const float* 
                                  const int* __restrict__ token_row, int N, int n_total,
                                  int n_real, int n_groups, int keep, int top,
                                  int* __restrict__ ids, float* __restrict__ weights,
-                                 int* __restrict__ counts) {
+                                 int* __restrict__ counts, int flags) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ float smem[];
@@ -151,7 +173,7 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, const float* 
     }
     route_token(logits + (int64_t)n * n_total, corr,
                 smem + (size_t)warp * (2 * n_total + 2 * n_groups), n_total, n_real, n_groups, keep,
-                top, lane, ids + (int64_t)n * top, weights + (int64_t)n * top, counts);
+                top, lane, ids + (int64_t)n * top, weights + (int64_t)n * top, counts, flags);
 }
 
 // Steps of few tokens (decode): ONE CTA routes every token, counts, plans the tiles, gives every
@@ -167,7 +189,7 @@ moe_route_small_kernel(const float* __restrict__ logits, const float* __restrict
                        float* __restrict__ weights, int* __restrict__ meta, int max_tiles,
                        int tile_rows, int* __restrict__ pair_token, int* __restrict__ pair_place,
                        const __nv_bfloat16* __restrict__ x, int64_t ldx, int K,
-                       __nv_bfloat16* __restrict__ rows_out) {
+                       __nv_bfloat16* __restrict__ rows_out, int flags) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ float smem[];
@@ -190,7 +212,7 @@ moe_route_small_kernel(const float* __restrict__ logits, const float* __restrict
         }
         route_token(logits + (int64_t)n * n_total, corr, smem + (size_t)warp * per_warp, n_total,
                     n_real, n_groups, keep, top, lane, ids + (int64_t)n * top,
-                    weights + (int64_t)n * top, counts);
+                    weights + (int64_t)n * top, counts, flags);
     }
     __syncthreads();
     for (int e = tid; e <= n_real; e += blockDim.x) {
@@ -280,16 +302,18 @@ __global__ void moe_scatter_kernel(const int* __restrict__ ids, int n_pairs, int
     pair_place[i] = place;
 }
 
-// grid (ceil(F / MOE_TN), max_tiles).  GATED: W is [E, 2 F, K] (gate rows, then up rows),
-// Y[place, f] = silu(x . gate_f) * (x . up_f) with x = X[pair_token[place]]; else W is
-// [E, F, K], Y[place, f] = X[place] . w_f.
-template <typename TIn, typename TOut, bool GATED>
+// grid (ceil(F / MOE_TN), max_tiles).  MODE 1 (gated): W is [E, 2 F, K] (gate rows, then up
+// rows), Y[place, f] = silu(x . gate_f) * (x . up_f) with x = X[pair_token[place]].  MODE 2
+// (an expert without a gate): W is [E, F, K], Y[place, f] = relu(x . w_f)^2 with the same
+// gathered x.  MODE 0: W is [E, F, K], Y[place, f] = X[place] . w_f.
+template <typename TIn, typename TOut, int MODE>
 __global__ void __launch_bounds__(256)
 moe_product_kernel(const TIn* __restrict__ X, int64_t ldx, const TIn* __restrict__ W,
                    TOut* __restrict__ Y, int64_t ldy, const int* __restrict__ meta,
                    const int* __restrict__ pair_token, int F, int K) {
     pdl_wait();
     pdl_trigger();
+    constexpr bool GATED = MODE == 1, GATHER = MODE != 0;
     if ((int)blockIdx.y >= meta[0]) return;
     const int* tile = meta + 1 + 3 * blockIdx.y;
     const int expert = tile[0], row0 = tile[1], rows = tile[2];
@@ -297,7 +321,7 @@ moe_product_kernel(const TIn* __restrict__ X, int64_t ldx, const TIn* __restrict
     __shared__ float Bs[GATED ? 2 : 1][MOE_TK][MOE_TN + 4];
     __shared__ int src_row[MOE_TM];
     const int tid = threadIdx.x;
-    if (tid < MOE_TM) src_row[tid] = tid < rows ? (GATED ? pair_token[row0 + tid] : row0 + tid) : -1;
+    if (tid < MOE_TM) src_row[tid] = tid < rows ? (GATHER ? pair_token[row0 + tid] : row0 + tid) : -1;
     __syncthreads();
     const int f0 = blockIdx.x * MOE_TN;
     const TIn* We = W + (int64_t)expert * (GATED ? 2 : 1) * F * K;
@@ -353,6 +377,8 @@ moe_product_kernel(const TIn* __restrict__ X, int64_t ldx, const TIn* __restrict
             if (GATED) {
                 const float g = y, u = acc[GATED ? 1 : 0][i][j];
                 y = g / (1.0f + expf(-g)) * u;
+            } else if (MODE == 2) {
+                y = y > 0.f ? y * y : 0.f;
             }
             Y[(int64_t)(row0 + r) * ldy + f] = from_float<TOut>(y);
         }
@@ -452,7 +478,7 @@ SLLM_EXPORT int sllm_moe_tile_rows() { return MOE_TM; }
 SLLM_EXPORT int sllm_moe_route(const float* logits, const float* corr, const int* token_row,
                                int n_tokens, int n_total, int n_real, int n_groups, int keep,
                                int top, int* ids, float* weights, int* work, int max_tiles,
-                               int tile_rows, int* pair_token, int* pair_place,
+                               int tile_rows, int* pair_token, int* pair_place, int flags,
                                cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (n_total <= 0 || n_real < 0 || n_real > n_total || top < 1 || top > MOE_MAX_TOP ||
@@ -468,7 +494,7 @@ SLLM_EXPORT int sllm_moe_route(const float* logits, const float* corr, const int
                                       dim3(32 * warps),
                                       (size_t)warps * (2 * n_total + 2 * n_groups) * sizeof(float),
                                       stream, logits, corr, token_row, n_tokens, n_total, n_real,
-                                      n_groups, keep, top, ids, weights, counts);
+                                      n_groups, keep, top, ids, weights, counts, flags);
     if (err != cudaSuccess) return (int)err;
     if (n_real == 0) return 0;
     err = sllm_launch_pdl(moe_plan_kernel, dim3(1), dim3(256), 0, stream, (const int*)counts,
@@ -491,7 +517,7 @@ SLLM_EXPORT int sllm_moe_route_small(const float* logits, const float* corr, con
                                      int n_tokens, int n_total, int n_real, int n_groups, int keep,
                                      int top, int* ids, float* weights, int* meta, int max_tiles,
                                      int tile_rows, int* pair_token, int* pair_place,
-                                     const void* x, int64_t ldx, int K, void* rows_out,
+                                     const void* x, int64_t ldx, int K, void* rows_out, int flags,
                                      cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (n_total <= 0 || n_real < 0 || n_real > n_total || top < 1 || top > MOE_MAX_TOP ||
@@ -507,11 +533,12 @@ SLLM_EXPORT int sllm_moe_route_small(const float* logits, const float* corr, con
                                 (size_t)smem, stream, logits, corr, token_row, n_tokens, n_total,
                                 n_real, n_groups, keep, top, ids, weights, meta, max_tiles,
                                 tile_rows, pair_token, pair_place, (const __nv_bfloat16*)x, ldx, K,
-                                (__nv_bfloat16*)rows_out);
+                                (__nv_bfloat16*)rows_out, flags);
 }
 
-// dtype: 0 = float32 operands, 1 = bfloat16 operands.  gated: Y has the operands' dtype; else Y
-// is float32.
+// dtype: 0 = float32 operands, 1 = bfloat16 operands.  gated 1 (silu(gate) * up) and 2 (squared
+// relu of one matrix): rows gathered through pair_token, Y has the operands' dtype; 0: Y is
+// float32.
 SLLM_EXPORT int sllm_moe_product(const void* X, int64_t ldx, const void* W, void* Y, int64_t ldy,
                                  const int* meta, const int* pair_token, int F, int K,
                                  int max_tiles, int gated, int dtype, cudaStream_t stream) {
@@ -520,20 +547,29 @@ SLLM_EXPORT int sllm_moe_product(const void* X, int64_t ldx, const void* W, void
     dim3 grid((F + MOE_TN - 1) / MOE_TN, max_tiles);
     typedef __nv_bfloat16 bf16;
     cudaError_t err;
-    if (dtype == 0 && gated)
-        err = sllm_launch_pdl(moe_product_kernel<float, float, true>, grid, dim3(256), 0, stream,
+    if (gated < 0 || gated > 2) return (int)cudaErrorInvalidValue;
+    if (dtype == 0 && gated == 1)
+        err = sllm_launch_pdl(moe_product_kernel<float, float, 1>, grid, dim3(256), 0, stream,
+                              (const float*)X, ldx, (const float*)W, (float*)Y, ldy, meta,
+                              pair_token, F, K);
+    else if (dtype == 0 && gated == 2)
+        err = sllm_launch_pdl(moe_product_kernel<float, float, 2>, grid, dim3(256), 0, stream,
                               (const float*)X, ldx, (const float*)W, (float*)Y, ldy, meta,
                               pair_token, F, K);
     else if (dtype == 0)
-        err = sllm_launch_pdl(moe_product_kernel<float, float, false>, grid, dim3(256), 0, stream,
+        err = sllm_launch_pdl(moe_product_kernel<float, float, 0>, grid, dim3(256), 0, stream,
                               (const float*)X, ldx, (const float*)W, (float*)Y, ldy, meta,
                               pair_token, F, K);
-    else if (dtype == 1 && gated)
-        err = sllm_launch_pdl(moe_product_kernel<bf16, bf16, true>, grid, dim3(256), 0, stream,
+    else if (dtype == 1 && gated == 1)
+        err = sllm_launch_pdl(moe_product_kernel<bf16, bf16, 1>, grid, dim3(256), 0, stream,
+                              (const bf16*)X, ldx, (const bf16*)W, (bf16*)Y, ldy, meta, pair_token,
+                              F, K);
+    else if (dtype == 1 && gated == 2)
+        err = sllm_launch_pdl(moe_product_kernel<bf16, bf16, 2>, grid, dim3(256), 0, stream,
                               (const bf16*)X, ldx, (const bf16*)W, (bf16*)Y, ldy, meta, pair_token,
                               F, K);
     else if (dtype == 1)
-        err = sllm_launch_pdl(moe_product_kernel<bf16, float, false>, grid, dim3(256), 0, stream,
+        err = sllm_launch_pdl(moe_product_kernel<bf16, float, 0>, grid, dim3(256), 0, stream,
                               (const bf16*)X, ldx, (const bf16*)W, (float*)Y, ldy, meta,
                               pair_token, F, K);
     else

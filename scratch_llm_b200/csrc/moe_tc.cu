@@ -66,7 +66,8 @@ __device__ __forceinline__ void store_row32(float* dst, const float (&o)[32], in
 // n_out: output features per expert (GATED: the gated size F, W holds 2 F rows per expert).
 // Tile index t: row tile t % n_row_tiles (fastest, so that an expert's row tiles, which share
 // its weights, run side by side), feature block t / n_row_tiles.
-template <bool GATED, typename TOut>
+// SQRELU (not gated): the stored value is relu(y)^2, an expert without a gate.
+template <bool GATED, typename TOut, bool SQRELU = false>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 moe_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
               TOut* __restrict__ Y, const int* __restrict__ meta, int n_out, int K, int64_t ldy,
@@ -187,7 +188,10 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
                     if (r < rows && col < n_out) {
                         float o[32];
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(v[i]);
+                        for (int i = 0; i < 32; ++i) {
+                            o[i] = __uint_as_float(v[i]);
+                            if (SQRELU) o[i] = o[i] > 0.f ? o[i] * o[i] : 0.f;
+                        }
                         store_row32(dst + col, o, n_out - col, aligned);
                     }
                 }
@@ -298,7 +302,8 @@ SLLM_EXPORT int sllm_moe_gather_rows(const void* x, int64_t ldx, const int* pair
 }
 
 // X: bfloat16 [n_rows, K] (rows in the sorted order), W: bfloat16 [experts * rows per expert, K]
-// contiguous, Y: [n_rows, n_out] bfloat16 (gated) or float32.  meta: the tile list of tiles of
+// contiguous, Y: [n_rows, n_out] bfloat16 (gated 1: silu(gate) * up of [gate rows; up rows];
+// gated 2: relu(x w)^2 of one matrix) or float32 (gated 0).  meta: the tile list of tiles of
 // 128 rows; max_tiles bounds its length.
 SLLM_EXPORT int sllm_moe_tc_product(const void* X, int64_t n_rows, const void* W, int n_experts,
                                     void* Y, const int* meta, int n_out, int K, int max_tiles,
@@ -314,16 +319,23 @@ SLLM_EXPORT int sllm_moe_tc_product(const void* X, int64_t n_rows, const void* W
             cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
             return (int)cudaErrorUnknown;
     }
-    const int64_t w_rows = (int64_t)n_experts * (gated ? 2 : 1) * n_out;
+    if (gated < 0 || gated > 2) return (int)cudaErrorInvalidValue;
+    const int64_t w_rows = (int64_t)n_experts * (gated == 1 ? 2 : 1) * n_out;
     CUtensorMap map_x, map_w;
     if (!make_map(&map_x, X, n_rows, K, K) || !make_map(&map_w, W, w_rows, K, K))
         return (int)cudaErrorNotSupported;
-    const int tiles_n = gated ? (n_out + 127) / 128 : (n_out + TN - 1) / TN;
+    const int tiles_n = gated == 1 ? (n_out + 127) / 128 : (n_out + TN - 1) / TN;
     const int64_t total = (int64_t)max_tiles * tiles_n;
     if (total > 0x7fffffff) return (int)cudaErrorInvalidValue;
     dim3 grid((unsigned)(total < n_sm ? total : n_sm));
     cudaError_t e;
-    if (gated) {
+    if (gated == 2) {
+        e = cudaFuncSetAttribute(moe_tc_kernel<false, bf16, true>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        moe_tc_kernel<false, bf16, true><<<grid, TC_THREADS, TC_SMEM, stream>>>(
+            map_x, map_w, (bf16*)Y, meta, n_out, K, (int64_t)n_out, tiles_n, max_tiles);
+    } else if (gated) {
         e = cudaFuncSetAttribute(moe_tc_kernel<true, bf16>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM);
         if (e != cudaSuccess) return (int)e;

@@ -275,9 +275,39 @@ __global__ void param_act_vec_kernel(const T* __restrict__ x, T* __restrict__ ou
     }
 }
 
+// out[n] = [a[n]; b[n]] rounded to T: two 32-bit streams side by side, as the operand of a
+// product over both.
+template <typename T>
+__global__ void concat_cast_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                   T* __restrict__ out, int64_t total, int d) {
+    pdl_wait();
+    pdl_trigger();
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t n = i / (2 * d);
+        const int e = (int)(i - n * 2 * d);
+        out[i] = from_float<T>(e < d ? a[n * d + e] : b[n * d + e - d]);
+    }
+}
+
 }  // namespace sllm
 
 using namespace sllm;
+
+SLLM_EXPORT int sllm_concat_cast(const float* a, const float* b, void* out, int n_rows, int d,
+                                 int dtype, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (d <= 0) return (int)cudaErrorInvalidValue;
+    const int64_t total = (int64_t)n_rows * 2 * d;
+    const int blocks = (int)((total + 255) / 256 > 4096 ? 4096 : (total + 255) / 256);
+    if (dtype == 0)
+        return (int)sllm_launch_pdl(concat_cast_kernel<float>, dim3(blocks), dim3(256), 0, stream,
+                                    a, b, (float*)out, total, d);
+    if (dtype == 1)
+        return (int)sllm_launch_pdl(concat_cast_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0,
+                                    stream, a, b, (__nv_bfloat16*)out, total, d);
+    return (int)cudaErrorInvalidValue;
+}
 
 static int row_threads(int d) {
     int t = 32;

@@ -16,7 +16,7 @@ import torch
 from ..config.spec import ModelSpec, PartSpec
 from ..kernels import ops
 from ..parts import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, SIDE_INPUTS,
-                     TOKEN_MIXES, BuildContext, CacheView, KVSpec, StateSpec, make)
+                     STREAM_JOINS, TOKEN_MIXES, BuildContext, CacheView, KVSpec, StateSpec, make)
 from ..parts.linear import Linear
 from ..parts.stream import Current, Normed, StreamSink
 from ..weights.loader import ParamSpec
@@ -97,6 +97,13 @@ class DecoderModel:
             block.cache_owner = next((built[r] for r, k in roles.items() if k == "mixer"), None)
             self.blocks.append(block)
         self._positions = list(positions.values())
+        # joins of the stream with the embedding output that some runs ask for
+        self.joins = []
+        for join in spec.joins:
+            part = make(STREAM_JOINS, "stream join", join.part)
+            self.joins.append(part)
+            self._named_parts.append((join.prefix, part))
+        self._keeps_first = any(run.join is not None for run in spec.order)
         # per run: the (norm, part) the NEXT run's block starts with, for blocks that ask
         self._next_entry: list = []
         for i, run in enumerate(spec.order):
@@ -130,6 +137,8 @@ class DecoderModel:
             seen.setdefault(id(block), block)
             for part in block.parts.values():
                 seen.setdefault(id(part), part)
+        for part in self.joins:
+            seen.setdefault(id(part), part)
         seen.setdefault(id(self.final_norm), self.final_norm)
         return list(seen.values())
 
@@ -274,7 +283,17 @@ class DecoderModel:
         resid = torch.empty((batch.n_tokens, s.hidden_size), dtype=torch.float32,
                             device=self.ctx.device)
         pending = self._embed(batch, resid)
+        first = None
+        if self._keeps_first:
+            if pending is not None:
+                raise ValueError("a model that joins the stream with the embedding output needs "
+                                 "an embedding that leaves nothing pending")
+            first = resid.clone()
         for i, run in enumerate(s.order):
+            if run.join is not None:
+                if pending is not None:
+                    raise ValueError("a join takes a stream with nothing pending")
+                resid = self.joins[run.join].forward(resid, first)
             pages, group = cache.entry_pages(run.cache)
             state, block_state = self._states_of(cache, run.cache)
             view = CacheView(pages=pages,

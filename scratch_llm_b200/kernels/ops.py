@@ -44,6 +44,7 @@ EXTRA_LIBRARIES: dict[str, tuple[tuple[str, ...], tuple[str, ...]]] = {
     "sllm_tanh_norm": (("tanh_norm.cu",), ()),
     "sllm_moe": (("moe.cu",), ()),
     "sllm_moe_tc": (("moe_tc.cu",), ()),
+    "sllm_latent_attention": (("latent_attention.cu",), ()),
 }
 
 
@@ -90,6 +91,8 @@ def attention_tc_supports(n_heads: int, n_kv_heads: int, head_dim: int, page_siz
 
 #: the tensor-core attention kernels take head sizes up to this; larger ones use the CUDA cores
 MMA_MAX_HEAD_DIM = 256
+#: the CUDA-core attention kernel takes head sizes up to this (its tiles fill shared memory)
+SIMT_MAX_HEAD_DIM = 640
 
 _loaded: dict[str, ctypes.CDLL] = {}
 
@@ -551,6 +554,17 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_row: torch.T
 
 # -------------------------------------------------------------------------------- attention
 
+def _page_planes(pages: torch.Tensor, n_kv_heads: int, page_size: int, head_dim: int) -> int:
+    """Pages are [n_pages, planes, kv heads, page size, head size]: two planes hold keys, then
+    values; one plane holds one vector per token that is its key and, by its leading entries,
+    its value (a cache of latents).  Returns the number of planes."""
+    if pages.dim() != 5 or pages.shape[1] not in (1, 2) \
+            or pages.shape[2:] != (n_kv_heads, page_size, head_dim):
+        raise KernelError(f"pages must be [n_pages, 1 or 2, {n_kv_heads}, {page_size}, "
+                          f"{head_dim}], got {list(pages.shape)}")
+    return int(pages.shape[1])
+
+
 def _head_vectors(slopes: torch.Tensor | None, sinks: torch.Tensor | None, n_heads: int) -> None:
     for t, name in ((slopes, "slopes"), (sinks, "sinks")):
         if t is not None:
@@ -580,18 +594,17 @@ def attention_simt(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tens
     if q.stride(1) != 1 or out.stride(1) != 1 or q.shape[1] != n_heads * head_dim \
             or out.shape != q.shape:
         raise KernelError("attention q/out layout")
-    if pages.shape[1:] != (2, n_kv_heads, page_size, head_dim):
-        raise KernelError(f"pages must be [n_pages, 2, {n_kv_heads}, {page_size}, {head_dim}], "
-                          f"got {list(pages.shape)}")
-    if not 1 <= head_dim <= 512:
-        raise KernelError(f"head size {head_dim}: the CUDA-core attention kernel takes 1 to 512")
+    planes = _page_planes(pages, n_kv_heads, page_size, head_dim)
+    if not 1 <= head_dim <= SIMT_MAX_HEAD_DIM:
+        raise KernelError(f"head size {head_dim}: the CUDA-core attention kernel takes 1 to "
+                          f"{SIMT_MAX_HEAD_DIM}")
     lib = _load(*attention_library(head_dim))
     _check(lib.sllm_attn_simt(
         _ptr(q), c_int64(q.stride(0)), _ptr(pages), _ptr(block_table),
         c_int(block_table.stride(0)), c_int(page_size), _ptr(row_start), _ptr(row_pos0),
         _ptr(out), c_int64(out.stride(0)), c_int(n_rows), c_int(max_new), c_int(n_heads),
         c_int(n_kv_heads), c_float(scale), c_int(window or 0), _ptr(slopes), _ptr(sinks),
-        c_int(_code(q.dtype)), _stream()), "attention_simt")
+        c_int(planes), c_int(_code(q.dtype)), _stream()), "attention_simt")
     return out
 
 
@@ -628,9 +641,7 @@ def attention_mma(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tenso
     if q.stride(1) != 1 or out.stride(1) != 1 or q.shape[1] != n_heads * head_dim \
             or out.shape != q.shape:
         raise KernelError("attention q/out layout")
-    if pages.shape[1:] != (2, n_kv_heads, page_size, head_dim):
-        raise KernelError(f"pages must be [n_pages, 2, {n_kv_heads}, {page_size}, {head_dim}], "
-                          f"got {list(pages.shape)}")
+    planes = _page_planes(pages, n_kv_heads, page_size, head_dim)
     if head_dim % 16 or not 16 <= head_dim <= MMA_MAX_HEAD_DIM:
         raise KernelError(f"head size {head_dim}: the tensor-core attention kernels take "
                           f"multiples of 16 up to {MMA_MAX_HEAD_DIM}")
@@ -653,7 +664,7 @@ def attention_mma(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tenso
         c_int(n_heads), c_int(n_kv_heads), c_float(scale), c_int(window or 0),
         c_int(int(split)), c_int(n_splits), _ptr(scratch), c_int64(n_tokens), _ptr(slopes),
         _ptr(sinks), _ptr(gate), c_int64(gate.stride(0) if gate is not None else 0),
-        _ptr(counters), _stream()), "attention_mma")
+        _ptr(counters), c_int(planes), _stream()), "attention_mma")
     return out
 
 
@@ -788,9 +799,7 @@ def attention_tc(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor
     if q.stride(1) != 1 or out.stride(1) != 1 or q.shape[1] != n_heads * head_dim \
             or out.shape != q.shape:
         raise KernelError("attention q/out layout")
-    if pages.shape[1:] != (2, n_kv_heads, page_size, head_dim):
-        raise KernelError(f"pages must be [n_pages, 2, {n_kv_heads}, {page_size}, {head_dim}], "
-                          f"got {list(pages.shape)}")
+    planes = _page_planes(pages, n_kv_heads, page_size, head_dim)
     lib = _load(*attention_tc_library(head_dim))
     common = (_ptr(q), c_int64(q.stride(0)), c_int64(q.shape[0]), _ptr(pages),
               c_int64(pages.shape[0]), _ptr(block_table), c_int(block_table.stride(0)),
@@ -798,10 +807,12 @@ def attention_tc(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor
               c_int(max_new), _ptr(out), c_int64(out.stride(0)), c_int(n_heads), c_int(n_kv_heads),
               c_float(scale))
     if biased:
+        if planes != 2:
+            raise KernelError("the biased tcgen05 attention takes pages of keys and values")
         _check(lib.sllm_attn_tc_biased(*common, c_int(window or 0), _ptr(slopes), _ptr(sinks),
                                        _stream()), "attention_tc")
     else:
-        _check(lib.sllm_attn_tc(*common, _stream()), "attention_tc")
+        _check(lib.sllm_attn_tc(*common, c_int(planes), _stream()), "attention_tc")
     return out
 
 
@@ -1312,16 +1323,25 @@ def moe_max_tiles(n_tokens: int, top: int, n_real: int, tile_rows: int) -> int:
 MOE_SMALL_PAIRS = 64
 
 
+#: router variants (bits of ``flags`` in :func:`moe_route`)
+MOE_SIGMOID, MOE_GROUP_TOP2, MOE_RAW_WEIGHTS = 1, 2, 4
+#: what a grouped product does with its rows (``gated`` in :func:`moe_product`)
+MOE_PLAIN, MOE_GATED, MOE_SQRELU = 0, 1, 2
+
+
 def moe_route(logits: torch.Tensor, correction: torch.Tensor, token_row: torch.Tensor | None,
               n_real: int, n_groups: int, keep: int, top: int, tile_rows: int | None = None,
-              gather_from: torch.Tensor | None = None):
+              gather_from: torch.Tensor | None = None, flags: int = 0):
     """Route every token of ``logits`` (float32 [N, outputs]) and sort the (token, choice) pairs
     by expert (csrc/moe.cu).  Returns ``(ids [N, top], weights [N, top], pair_token [N * top],
     pair_place [N * top], meta, max_tiles, rows)``; ``meta`` is the tile list of the grouped
     products, in tiles of ``tile_rows`` rows (default: what :func:`moe_product` takes).
     ``gather_from`` (bfloat16 [N, K], K % 8 == 0): the caller wants the tokens' rows in the
     sorted order; ``rows`` is that copy where the router made it on its way (steps of few tokens,
-    where one CTA does everything in one launch), else None (:func:`moe_gather_rows` makes it)."""
+    where one CTA does everything in one launch), else None (:func:`moe_gather_rows` makes it).
+    ``flags``: ``MOE_SIGMOID`` scores are ``sigmoid(z)`` instead of a softmax over the outputs;
+    ``MOE_GROUP_TOP2`` a group's score is the sum of its two largest choice scores instead of its
+    largest; ``MOE_RAW_WEIGHTS`` the weights are the chosen scores, not divided by their sum."""
     _need(logits, torch.float32, "logits")
     _need(correction, torch.float32, "correction")
     n, n_total = logits.shape
@@ -1353,8 +1373,8 @@ def moe_route(logits: torch.Tensor, correction: torch.Tensor, token_row: torch.T
             c_int(n_real), c_int(n_groups), c_int(keep), c_int(top), _ptr(ids), _ptr(weights),
             _ptr(meta), c_int(max_tiles), c_int(tile_rows), _ptr(pair_token), _ptr(pair_place),
             _ptr(gather_from), c_int64(gather_from.stride(0) if gather_from is not None else 0),
-            c_int(gather_from.shape[1] if gather_from is not None else 0), _ptr(rows), _stream()),
-            "moe_route_small")
+            c_int(gather_from.shape[1] if gather_from is not None else 0), _ptr(rows),
+            c_int(flags), _stream()), "moe_route_small")
         return ids, weights, pair_token, pair_place, meta, max_tiles, rows
     # one zero fill: the experts' counters (with the offsets, cursors and tile list behind them)
     # and the places' tokens (places that no pair takes name token 0)
@@ -1364,30 +1384,33 @@ def moe_route(logits: torch.Tensor, correction: torch.Tensor, token_row: torch.T
     _check(lib.sllm_moe_route(
         _ptr(logits), _ptr(correction), _ptr(token_row), c_int(n), c_int(n_total), c_int(n_real),
         c_int(n_groups), c_int(keep), c_int(top), _ptr(ids), _ptr(weights), _ptr(work),
-        c_int(max_tiles), c_int(tile_rows), _ptr(pair_token), _ptr(pair_place), _stream()),
-        "moe_route")
+        c_int(max_tiles), c_int(tile_rows), _ptr(pair_token), _ptr(pair_place), c_int(flags),
+        _stream()), "moe_route")
     meta = work[3 * n_real + 1:]
     return ids, weights, pair_token, pair_place, meta, max_tiles, None
 
 
 def moe_product(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, meta: torch.Tensor,
-                pair_token: torch.Tensor, max_tiles: int, gated: bool) -> torch.Tensor:
-    """The grouped product of a routed feed-forward over the places of ``meta``.  ``gated``:
-    ``w`` [E, 2 F, K], ``out[place] = silu(x[token] gate^T) * (x[token] up^T)`` (the dtype of
-    ``x``); else ``w`` [E, F, K], ``out[place] = x[place] w^T`` in float32."""
+                pair_token: torch.Tensor, max_tiles: int, gated: bool | int) -> torch.Tensor:
+    """The grouped product of a routed feed-forward over the places of ``meta``.  ``gated``
+    True (``MOE_GATED``): ``w`` [E, 2 F, K], ``out[place] = silu(x[token] gate^T) * (x[token]
+    up^T)`` (the dtype of ``x``); ``MOE_SQRELU``: ``w`` [E, F, K], ``out[place] =
+    relu(x[token] w^T)^2`` (the dtype of ``x``); False: ``w`` [E, F, K], ``out[place] = x[place]
+    w^T`` in float32."""
+    gated = int(gated)
     _need(x, None, "x", contiguous=False)
     _need(w, x.dtype, "w")
     _need(out, x.dtype if gated else torch.float32, "out")
     _need(meta, torch.int32, "meta")
     _need(pair_token, torch.int32, "pair_token")
-    f = w.shape[1] // 2 if gated else w.shape[1]
+    f = w.shape[1] // 2 if gated == MOE_GATED else w.shape[1]
     k = w.shape[2]
     if x.stride(1) != 1 or x.shape[1] != k or out.shape[1] != f \
             or out.shape[0] < pair_token.numel():
         raise KernelError("moe_product shapes")
     _check(_core("sllm_moe").sllm_moe_product(
         _ptr(x), c_int64(x.stride(0)), _ptr(w), _ptr(out), c_int64(out.stride(0)), _ptr(meta),
-        _ptr(pair_token), c_int(f), c_int(k), c_int(max_tiles), c_int(int(gated)),
+        _ptr(pair_token), c_int(f), c_int(k), c_int(max_tiles), c_int(gated),
         c_int(_code(x.dtype)), _stream()), "moe_product")
     return out
 
@@ -1412,22 +1435,24 @@ def moe_gather_rows(x: torch.Tensor, pair_token: torch.Tensor, out: torch.Tensor
 
 
 def moe_tc_product(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, meta: torch.Tensor,
-                   max_tiles: int, gated: bool) -> torch.Tensor:
+                   max_tiles: int, gated: bool | int) -> torch.Tensor:
     """The grouped product on tcgen05 (csrc/moe_tc.cu) over the rows of ``x`` [places, K]
-    (bfloat16, in the sorted order) with tiles of 128 rows in ``meta``.  ``gated``: ``w``
-    [E, 2 F, K], ``out`` bfloat16 [places, F] = silu(gate) * up; else ``w`` [E, F, K] and ``out``
-    float32 [places, F]."""
+    (bfloat16, in the sorted order) with tiles of 128 rows in ``meta``.  ``gated`` True
+    (``MOE_GATED``): ``w`` [E, 2 F, K], ``out`` bfloat16 [places, F] = silu(gate) * up;
+    ``MOE_SQRELU``: ``w`` [E, F, K], ``out`` bfloat16 [places, F] = relu(x w^T)^2; False: ``w``
+    [E, F, K] and ``out`` float32 [places, F]."""
+    gated = int(gated)
     _need(x, torch.bfloat16, "x")
     _need(w, torch.bfloat16, "w")
     _need(out, torch.bfloat16 if gated else torch.float32, "out")
     _need(meta, torch.int32, "meta")
     e, rows, k = w.shape
-    f = rows // 2 if gated else rows
+    f = rows // 2 if gated == MOE_GATED else rows
     if x.shape[1] != k or out.shape != (x.shape[0], f) or k % 8:
         raise KernelError("moe_tc_product shapes")
     _check(_core("sllm_moe_tc").sllm_moe_tc_product(
         _ptr(x), c_int64(x.shape[0]), _ptr(w), c_int(e), _ptr(out), _ptr(meta), c_int(f),
-        c_int(k), c_int(max_tiles), c_int(int(gated)), _stream()), "moe_tc_product")
+        c_int(k), c_int(max_tiles), c_int(gated), _stream()), "moe_tc_product")
     return out
 
 
@@ -1485,4 +1510,122 @@ def delta_rule(act: torch.Tensor, ab: torch.Tensor, a_log: torch.Tensor, dt_bias
         _ptr(dt_bias), _ptr(state), _ptr(row_start), _ptr(row_slot), _ptr(out), c_int(n_rows),
         c_int(max_new), c_int(n_heads), c_int(n_kv_heads), c_int(value_dim), c_int(_code(act.dtype)), _stream()),
         "delta_rule")
+    return out
+
+
+# ------------------------------------------------------------------------ latent attention
+
+def latent_prep(a: torch.Tensor, q_rank: int, kv_col: int, kv_rank: int, rot_dim: int,
+                q_gain: torch.Tensor, kv_gain: torch.Tensor, eps: float, positions: torch.Tensor,
+                token_row: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, cq: torch.Tensor,
+                pages: torch.Tensor, block_table: torch.Tensor, page_size: int,
+                write: bool) -> torch.Tensor:
+    """What a latent attention does with its down projections ``a`` [N, ...] (csrc/
+    latent_attention.cu): ``cq`` [N, q_rank] gets the RMS-normed query latent (columns 0 ..
+    q_rank of ``a``, times ``q_gain``); the page place of every token gets the RMS-normed
+    key/value latent (columns kv_col .. kv_col + kv_rank, times ``kv_gain``), behind it the
+    shared key part (the next ``rot_dim`` columns) with its first ``2 * cos.shape[1]`` entries
+    rotated by the token's position (entry i pairs with entry i + half), then zeros up to the
+    pages' vector size.  ``pages``: [n_pages, 1, 1, page_size, Dp]."""
+    _need(a, None, "a", contiguous=False)
+    _need(cq, a.dtype, "cq")
+    _need(pages, a.dtype, "pages")
+    _need(q_gain, torch.float32, "q_gain")
+    _need(kv_gain, torch.float32, "kv_gain")
+    _need(positions, torch.int32, "positions")
+    _need(token_row, torch.int32, "token_row")
+    _need(cos, torch.float32, "cos")
+    _need(sin, torch.float32, "sin")
+    _need(block_table, torch.int32, "block_table", contiguous=False)
+    n = a.shape[0]
+    rot_dims = 2 * cos.shape[1]
+    if a.stride(1) != 1 or a.shape[1] < max(q_rank, kv_col + kv_rank + rot_dim) \
+            or cq.shape != (n, q_rank) or q_gain.numel() != q_rank or kv_gain.numel() != kv_rank \
+            or sin.shape != cos.shape or rot_dims > rot_dim or block_table.stride(1) != 1:
+        raise KernelError("latent_prep shapes")
+    if pages.dim() != 5 or pages.shape[1:4] != (1, 1, page_size) \
+            or pages.shape[4] < kv_rank + rot_dim:
+        raise KernelError(f"pages must be [n_pages, 1, 1, {page_size}, at least "
+                          f"{kv_rank + rot_dim}], got {list(pages.shape)}")
+    _check(_core("sllm_latent_attention").sllm_latent_prep(
+        _ptr(a), c_int64(a.stride(0)), c_int(q_rank), c_int(kv_col), c_int(kv_rank),
+        c_int(rot_dim), _ptr(q_gain), _ptr(kv_gain), c_float(eps), _ptr(positions),
+        _ptr(token_row), _ptr(cos), _ptr(sin), c_int(rot_dims), _ptr(cq), _ptr(pages),
+        _ptr(block_table), c_int(block_table.stride(0)), c_int(page_size),
+        c_int(pages.shape[4]), c_int(int(write)), c_int(n), c_int(_code(a.dtype)), _stream()),
+        "latent_prep")
+    return cq
+
+
+def latent_q_rot(q: torch.Tensor, n_heads: int, dim: int, rot_dim: int, positions: torch.Tensor,
+                 cos: torch.Tensor, sin: torch.Tensor, out: torch.Tensor, kv_rank: int) -> torch.Tensor:
+    """``q`` [N, H * (dim + rot_dim)]: every head's last ``rot_dim`` entries, rotated like the
+    shared key part in :func:`latent_prep`, go to ``out`` [N, H * Dp] at columns ``h * Dp +
+    kv_rank`` on, zeros behind them up to Dp."""
+    _need(q, None, "q", contiguous=False)
+    _need(out, q.dtype, "out")
+    _need(positions, torch.int32, "positions")
+    _need(cos, torch.float32, "cos")
+    _need(sin, torch.float32, "sin")
+    n = q.shape[0]
+    if q.stride(1) != 1 or q.shape[1] != n_heads * (dim + rot_dim) or out.shape[0] != n \
+            or out.shape[1] % n_heads or out.shape[1] // n_heads < kv_rank + rot_dim \
+            or 2 * cos.shape[1] > rot_dim or sin.shape != cos.shape:
+        raise KernelError("latent_q_rot shapes")
+    _check(_core("sllm_latent_attention").sllm_latent_q_rot(
+        _ptr(q), c_int64(q.stride(0)), c_int(n_heads), c_int(dim), c_int(rot_dim),
+        _ptr(positions), _ptr(cos), _ptr(sin), c_int(2 * cos.shape[1]), _ptr(out),
+        c_int64(out.stride(0)), c_int(kv_rank), c_int(out.shape[1] // n_heads), c_int(n),
+        c_int(_code(q.dtype)), _stream()), "latent_q_rot")
+    return out
+
+
+def head_product(x: torch.Tensor, x_head_stride: int, w: torch.Tensor, out: torch.Tensor,
+                 out_head_stride: int) -> torch.Tensor:
+    """A product per head on the CUDA cores: ``out[n, h * out_head_stride + j] = sum_k x[n, h *
+    x_head_stride + k] * w[h, j, k]`` for ``w`` [H, J, K]; one fixed-order chain of fused
+    multiply-adds per output."""
+    _need(x, None, "x", contiguous=False)
+    _need(w, x.dtype, "w")
+    _need(out, x.dtype, "out", contiguous=False)
+    h, j, k = w.shape
+    n = x.shape[0]
+    if x.stride(1) != 1 or out.stride(1) != 1 or out.shape[0] != n \
+            or (h - 1) * x_head_stride + k > x.shape[1] \
+            or (h - 1) * out_head_stride + j > out.shape[1]:
+        raise KernelError("head_product shapes")
+    _check(_core("sllm_latent_attention").sllm_head_product(
+        _ptr(x), c_int64(x.stride(0)), c_int64(x_head_stride), _ptr(w), _ptr(out),
+        c_int64(out.stride(0)), c_int64(out_head_stride), c_int(n), c_int(h), c_int(j), c_int(k),
+        c_int(_code(x.dtype)), _stream()), "head_product")
+    return out
+
+
+def head_gate(x: torch.Tensor, gate: torch.Tensor, n_heads: int) -> torch.Tensor:
+    """``x`` [N, H * V] in place: head h of token n is multiplied by ``sigmoid(gate[n, h])``;
+    ``gate`` [N, H] may be a column slice of a wider buffer."""
+    _need(x, None, "x", contiguous=False)
+    _need(gate, x.dtype, "gate", contiguous=False)
+    n = x.shape[0]
+    if x.stride(1) != 1 or gate.stride(1) != 1 or gate.shape != (n, n_heads) \
+            or x.shape[1] % n_heads:
+        raise KernelError("head_gate shapes")
+    _check(_core("sllm_latent_attention").sllm_head_gate(
+        _ptr(x), c_int64(x.stride(0)), _ptr(gate), c_int64(gate.stride(0)), c_int(n_heads),
+        c_int(x.shape[1] // n_heads), c_int(n), c_int(_code(x.dtype)), _stream()), "head_gate")
+    return x
+
+
+def concat_cast(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out[n] = [a[n]; b[n]]`` rounded to the dtype of ``out``, for float32 ``a`` and ``b``
+    [N, d] and ``out`` [N, 2 d]."""
+    _need(a, torch.float32, "a")
+    _need(b, torch.float32, "b")
+    _need(out, None, "out")
+    n, d = a.shape
+    if b.shape != (n, d) or out.shape != (n, 2 * d):
+        raise KernelError("concat_cast shapes")
+    _check(_core("sllm_stream_ops").sllm_concat_cast(
+        _ptr(a), _ptr(b), _ptr(out), c_int(n), c_int(d), c_int(_code(out.dtype)), _stream()),
+        "concat_cast")
     return out

@@ -17,6 +17,8 @@ Mixer              ``forward(x, batch, cache, write, position) -> [N, hidden]``;
                    caches through ``kv_spec()`` (paged keys and values) and ``state_spec()``
                    (fixed-size state per request)
 FeedForward        ``forward(x) -> [N, hidden]``
+StreamJoin         ``forward(resid, first) -> resid``: the stream joined with the embedding
+                   output, before a run that the model's run order marks
 Block              ``forward(resid, pending, batch, cache, write) -> pending``: the arrangement
                    of a layer's parts around the residual stream; its ``ROLES`` says which
                    parts it has (role -> kind of part), and it is built with one keyword
@@ -50,11 +52,14 @@ class BuildContext:
 @dataclass(frozen=True)
 class KVSpec:
     """Paged keys and values one cache entry needs per token.  ``window`` None keeps every key;
-    a number keeps the last ``window`` keys and lets older pages be given back."""
+    a number keeps the last ``window`` keys and lets older pages be given back.  ``planes`` 2: a
+    page holds keys, then values; 1: one vector per token and kv head, which is its key and, by
+    its leading entries, its value (a cache of latents)."""
 
     n_kv_heads: int
     head_dim: int
     window: int | None = None
+    planes: int = 2
 
 
 @dataclass(frozen=True)
@@ -74,7 +79,7 @@ StateSpecs = StateSpec | tuple[StateSpec, ...] | None
 class CacheView:
     """What one run of a layer sees of the cache in this step."""
 
-    pages: torch.Tensor | None = None        # [n_pages, 2, n_kv_heads, page_size, head_dim]
+    pages: torch.Tensor | None = None        # [n_pages, planes, n_kv_heads, page_size, head_dim]
     block_table: torch.Tensor | None = None  # int32 [rows, max_pages]; -1 where no page is held
     page_size: int = 0
     # [n_slots, *StateSpec.shape], or a tuple of such tensors for a mixer with several states
@@ -155,6 +160,16 @@ class SideInput(Part):
     ids, positions or rows) beside the stream: ``forward(x, batch) -> [N, hidden]``."""
 
     def forward(self, x: torch.Tensor, batch: "StepBatch") -> torch.Tensor:
+        raise NotImplementedError
+
+
+class StreamJoin(Part):
+    """Something that replaces the residual stream, between two runs of layers, by a function of
+    the stream and of the embedding output (what the embedding left in the stream before the
+    first layer): ``forward(resid, first) -> resid`` on 32-bit [N, hidden] tensors; the result
+    may be a new tensor.  A model's run order says before which runs a join happens."""
+
+    def forward(self, resid: torch.Tensor, first: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
 

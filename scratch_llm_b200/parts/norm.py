@@ -25,10 +25,11 @@ class RMSNorm(Norm):
     #: product after it may apply it (scratch_llm_b200.parts.stream)
     deferrable = True
 
-    def __init__(self, size: int, eps: float, name: str = "weight") -> None:
+    def __init__(self, size: int, eps: float, name: str = "weight", offset: float = 0.0) -> None:
         """``name``: the gain's tensor name below the part's prefix; "" if the prefix itself is
-        the tensor's name."""
-        self.size, self.eps, self.name = size, float(eps), name
+        the tensor's name.  ``offset``: the gain is ``offset + w`` of the stored ``w`` (1.0 for
+        gains that are stored around zero), formed once at load in 32-bit."""
+        self.size, self.eps, self.name, self.offset = size, float(eps), name, float(offset)
         self.weight: torch.Tensor | None = None
         self.dtype = torch.float32
 
@@ -37,6 +38,8 @@ class RMSNorm(Norm):
 
     def load(self, tensors: Mapping[str, torch.Tensor], ctx: BuildContext) -> None:
         self.weight = tensors[self.name].to(device=ctx.device, dtype=torch.float32).contiguous()
+        if self.offset:
+            self.weight += self.offset
         self.dtype = ctx.dtype
 
     def forward(self, resid: torch.Tensor, delta: torch.Tensor | None,

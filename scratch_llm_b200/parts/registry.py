@@ -15,6 +15,7 @@ NORMS: dict[str, Callable[..., Any]] = {}
 POSITION_ENCODINGS: dict[str, Callable[..., Any]] = {}
 SIDE_INPUTS: dict[str, Callable[..., Any]] = {}
 TOKEN_MIXES: dict[str, Callable[..., Any]] = {}
+STREAM_JOINS: dict[str, Callable[..., Any]] = {}
 BLOCKS: dict[str, Callable[..., Any]] = {}
 
 
@@ -35,6 +36,7 @@ register_norm = _register(NORMS, "norm")
 register_position_encoding = _register(POSITION_ENCODINGS, "position encoding")
 register_side_input = _register(SIDE_INPUTS, "side input")
 register_token_mix = _register(TOKEN_MIXES, "token mix")
+register_stream_join = _register(STREAM_JOINS, "stream join")
 register_block = _register(BLOCKS, "block")
 
 

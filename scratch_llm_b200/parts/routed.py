@@ -14,6 +14,12 @@ tensors.  Experts and the shared expert: ``W_down(silu(W_gate x) * (W_up x))`` w
 Tensors below the part's prefix: ``router``, ``correction``, ``e<i>.{gate,up,down}`` and
 ``shared.{gate,up,down}``.
 
+Variants for other designs, each a constructor argument: ``score="sigmoid"`` (s = sigmoid(z), every
+output by itself, instead of the softmax), ``group_score="top2"`` (a group's score is the sum of
+its two largest choice scores instead of its largest), ``renormalize=False`` (the weights are the
+chosen scores s themselves) and ``expert="sqrelu"`` (experts without a gate,
+``W_down(relu(W_up x)^2)``, tensors ``e<i>.{up,down}``).
+
 Nothing of a step is read on the host: the router's kernel sorts the (token, choice) pairs by
 expert on the device and the grouped products walk a tile list, so steps can be recorded into
 CUDA graphs.  Every product of a token is one chain over the reduction in ascending order and the
@@ -40,7 +46,9 @@ class RoutedExperts(FeedForward):
 
     def __init__(self, hidden_size: int, expert_size: int, experts: int, top: int,
                  identity: int = 0, groups: int = 1, keep_groups: int = 1,
-                 shared_size: int | None = None) -> None:
+                 shared_size: int | None = None, score: str = "softmax",
+                 group_score: str = "max", renormalize: bool = True,
+                 expert: str = "gated_silu") -> None:
         total = experts + identity
         if experts < 0 or identity < 0 or total < 1:
             raise ValueError("a router needs at least one output")
@@ -51,6 +59,15 @@ class RoutedExperts(FeedForward):
                              f"which {keep_groups} are kept")
         if keep_groups * (total // groups) < top:
             raise ValueError("the kept groups hold fewer outputs than are chosen")
+        if score not in ("softmax", "sigmoid") or group_score not in ("max", "top2") \
+                or expert not in ("gated_silu", "sqrelu"):
+            raise ValueError(f"unknown router or expert variant: score {score!r}, group_score "
+                             f"{group_score!r}, expert {expert!r}")
+        self.flags = (ops.MOE_SIGMOID if score == "sigmoid" else 0) \
+            | (ops.MOE_GROUP_TOP2 if group_score == "top2" else 0) \
+            | (0 if renormalize else ops.MOE_RAW_WEIGHTS)
+        #: what the experts' first grouped product does: silu(gate) * up, or relu(up)^2
+        self.first = ops.MOE_GATED if expert == "gated_silu" else ops.MOE_SQRELU
         self.hidden_size, self.expert_size = hidden_size, expert_size
         self.experts, self.identity, self.top = experts, identity, top
         self.groups, self.keep_groups = groups, keep_groups
@@ -76,7 +93,8 @@ class RoutedExperts(FeedForward):
         d, f, total = self.hidden_size, self.expert_size, self.experts + self.identity
         specs = {"router": ParamSpec((total, d)), "correction": ParamSpec((total,), "gain")}
         for e in range(self.experts):
-            specs[f"e{e}.gate"] = ParamSpec((f, d))
+            if self.first == ops.MOE_GATED:
+                specs[f"e{e}.gate"] = ParamSpec((f, d))
             specs[f"e{e}.up"] = ParamSpec((f, d))
             specs[f"e{e}.down"] = ParamSpec((d, f))
         if self.shared is not None:
@@ -89,10 +107,15 @@ class RoutedExperts(FeedForward):
         self.correction = tensors["correction"].to(device=ctx.device,
                                                    dtype=torch.float32).contiguous()
         if self.experts:
-            # [E, 2 F, d]: an expert's gate rows, then its up rows; [E, d, F]
-            self.gate_up = torch.stack([torch.cat([put(tensors[f"e{e}.gate"]),
-                                                   put(tensors[f"e{e}.up"])], 0)
-                                        for e in range(self.experts)]).contiguous()
+            # [E, 2 F, d]: an expert's gate rows, then its up rows (without a gate: [E, F, d]);
+            # [E, d, F]
+            if self.first == ops.MOE_GATED:
+                self.gate_up = torch.stack([torch.cat([put(tensors[f"e{e}.gate"]),
+                                                       put(tensors[f"e{e}.up"])], 0)
+                                            for e in range(self.experts)]).contiguous()
+            else:
+                self.gate_up = torch.stack([put(tensors[f"e{e}.up"])
+                                            for e in range(self.experts)]).contiguous()
             self.down = torch.stack([put(tensors[f"e{e}.down"])
                                      for e in range(self.experts)]).contiguous()
         if self.shared is not None:
@@ -105,7 +128,7 @@ class RoutedExperts(FeedForward):
         ids, weights, pair_token, pair_place, meta, max_tiles, rows = ops.moe_route(
             logits, self.correction, None, self.experts, self.groups, self.keep_groups, self.top,
             tile_rows=ops.MOE_TC_TILE_ROWS if tensor_cores else None,
-            gather_from=x if tensor_cores else None)
+            gather_from=x if tensor_cores else None, flags=self.flags)
         pairs = n * self.top
         y = torch.empty((max(pairs, 1), d), dtype=torch.float32, device=x.device)
         if self.experts:
@@ -115,10 +138,11 @@ class RoutedExperts(FeedForward):
                 if rows is None:     # (steps of few tokens: the router has copied them itself)
                     rows = ops.moe_gather_rows(x, pair_token, torch.empty(
                         (pairs, d), dtype=x.dtype, device=x.device))
-                ops.moe_tc_product(rows, self.gate_up, hidden, meta, max_tiles, gated=True)
+                ops.moe_tc_product(rows, self.gate_up, hidden, meta, max_tiles, gated=self.first)
                 ops.moe_tc_product(hidden, self.down, y, meta, max_tiles, gated=False)
             else:
-                ops.moe_product(x, self.gate_up, hidden, meta, pair_token, max_tiles, gated=True)
+                ops.moe_product(x, self.gate_up, hidden, meta, pair_token, max_tiles,
+                                gated=self.first)
                 ops.moe_product(hidden, self.down, y, meta, pair_token, max_tiles, gated=False)
         shared = self.shared.forward(x) if self.shared is not None else None
         out = torch.empty_like(x)
