@@ -136,6 +136,32 @@ def vobosun_config(name: str):
                    {"type": "attention", "mixer": mixer, "mlp": dense}]})
 
 
+def titedra_config(name: str):
+    """The Titedra design at the sizes of COMPARE_SIZES: four layers of latent attention (as many
+    heads, the head size as the unrotated part, a rotated part of 64, a query latent of three
+    quarters of the width, a key/value latent of 192: the cached vector has 256 entries, the
+    largest the tensor-core attention kernels take), with a dense, two routed and a dense
+    feed-forward.  A routed one has 16 ungated experts of a quarter of the dense size in four
+    groups of which two are kept, and a token uses 4.  The two middle layers form a loop of one
+    pass, so that the stream is joined with the embedding output once and as many layers run as
+    in the models beside it."""
+    from scratch_llm_b200.config import config_from_dict
+
+    z = COMPARE_SIZES[name]
+    dense = {"kind": "dense", "ff": z["ff"]}
+    routed = {"kind": "moe", "expert": {"ff": z["ff"] // 4},
+              "router": {"experts": 16, "top": 4, "groups": {"count": 4, "keep": 2}}}
+    mixer = {"heads": z["heads"], "dim": z["dim"], "rot_dim": 64, "vdim": z["dim"],
+             "q_rank": 3 * z["width"] // 4, "kv_rank": 192, "scale": (z["dim"] + 64) ** -0.5,
+             "rot": {"base": 1000000.0, "dims": 64}}
+    return config_from_dict({
+        "architecture": "Titedra", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+        "embedding": {"scale": 1.0}, "logit_scale": 1.0, "max_position": 8192,
+        "loop": {"start": 1, "stop": 3, "times": 1},
+        "layers": [{"type": "latent_attention", "mixer": mixer, "mlp": mlp}
+                   for mlp in (dense, routed, routed, dense)]})
+
+
 def engine_of(cfg, capacity_tokens: int, max_requests: int, page_size: int):
     """An engine for ``cfg`` with random weights drawn on the device, tensor by tensor."""
     import torch
@@ -165,10 +191,12 @@ def engine_of(cfg, capacity_tokens: int, max_requests: int, page_size: int):
 
 
 def compare_main(args) -> int:
-    """--compare nilevik | vobosun: prefill and decode throughput of that design beside the
-    engine's other models of equal size (for Vobosun: Nilevik, the closest one, a hybrid of
-    attention and a delta rule with normed branch outputs, and the Llama-style model), at the
-    sizes of COMPARE_SIZES.  One JSON line."""
+    """--compare nilevik | vobosun | titedra: prefill and decode throughput of that design beside
+    the engine's other models of equal size (for Vobosun: Nilevik, the closest one, a hybrid of
+    attention and a delta rule with normed branch outputs, and the Llama-style model; for
+    Titedra: Vobosun, the closest one, with norms around every branch, a partly rotated
+    attention and routed experts, and the Llama-style model), at the sizes of COMPARE_SIZES.
+    One JSON line."""
     import torch
 
     torch.cuda.set_device(0)
@@ -182,10 +210,16 @@ def compare_main(args) -> int:
             out["sizes"][name] = entry = {"layers": "attention, attention, delta, attention",
                                           **{k: v for k, v in COMPARE_SIZES[name].items()}}
             archs = list(zip(("nilevik", "llama"), compare_configs(name)))
-            if args.compare == "vobosun":
+            if args.compare in ("vobosun", "titedra"):
                 entry["vobosun_layers"] = ("attention + dense, general_delta + routed, "
                                            "attention + routed, attention + dense")
                 archs.insert(0, ("vobosun", vobosun_config(name)))
+            if args.compare == "titedra":
+                entry["titedra_layers"] = ("latent_attention + dense, 2 x (latent_attention + "
+                                           "routed) as a loop of one pass, latent_attention + "
+                                           "dense")
+                archs = [("titedra", titedra_config(name))] + \
+                    [a for a in archs if a[0] != "nilevik"]
             for arch, cfg in archs:
                 llm = engine_of(cfg, capacity, args.batch + 1, args.page_size)
                 with ClockSampler(0) as clk:
@@ -347,7 +381,7 @@ def main() -> int:
                     help="layer sizes (the default is the configuration the metric is quoted on)")
     ap.add_argument("--serve", type=int, default=0, metavar="N",
                     help="also run the continuous-batching workload with N requests")
-    ap.add_argument("--compare", default=None, choices=["nilevik", "vobosun"],
+    ap.add_argument("--compare", default=None, choices=["nilevik", "vobosun", "titedra"],
                     help="instead of the headline workload: prefill and decode throughput of "
                          "this design beside the Llama-style model of equal size")
     ap.add_argument("--compare-sizes", default=None, choices=sorted(COMPARE_SIZES),

@@ -104,6 +104,10 @@ class DecoderModel:
             self.joins.append(part)
             self._named_parts.append((join.prefix, part))
         self._keeps_first = any(run.join is not None for run in spec.order)
+        #: for looking into a model: called as ``stream_probe(run index, resid, pending)`` after
+        #: every run of a layer in steps that run eagerly (the stream is ``resid`` plus what is
+        #: pending, if anything is); None in normal use
+        self.stream_probe = None
         # per run: the (norm, part) the NEXT run's block starts with, for blocks that ask
         self._next_entry: list = []
         for i, run in enumerate(spec.order):
@@ -310,6 +314,8 @@ class DecoderModel:
                                         next_entry=self._next_entry[i])
             else:
                 pending = block.forward(resid, pending, batch, view, run.write)
+            if self.stream_probe is not None:
+                self.stream_probe(i, resid, pending)
         if batch.n_out == 0:
             return None
         if isinstance(pending, Normed):      # prepared by the last run: every row, in order
