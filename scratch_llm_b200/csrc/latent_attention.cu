@@ -16,6 +16,9 @@
 //   head_product    out[n, h, j] = sum_k x[n, h, k] * w[h, j, k] (a product per head; the
 //                   32-bit path's absorb and value products, one fixed-order chain per output)
 //   head_gate       x[n, h, :] *= sigmoid(gate[n, h])   (one gate per head)
+//   latent_small    steps of few tokens: a product per head with the output index last in the
+//                   matrix, with the rotated tail (the absorb product and latent_q_rot in one
+//                   launch) or with the gate (the value product and head_gate in one launch)
 //
 // The rotation pairs entry i with entry i + dims / 2 among the first `dims` entries of the rotated
 // part: (u, v) -> (u cos a - v sin a, v cos a + u sin a), a = position * frequency_i, from 32-bit
@@ -26,7 +29,8 @@
 namespace sllm {
 
 // a: [N, lda] with the query latent at column 0 (Rq entries) and the key/value latent at column
-// kv_col (R entries) followed by the shared key part (r entries).  One block per token.
+// kv_col (R entries) followed by the shared key part (r entries).  Two blocks per token: grid
+// (N, 2), one for the query latent and one for what is stored.
 template <typename T>
 __global__ void __launch_bounds__(256)
 latent_prep_kernel(const T* __restrict__ a, int64_t lda, int Rq, int kv_col, int R, int r,
@@ -41,14 +45,17 @@ latent_prep_kernel(const T* __restrict__ a, int64_t lda, int Rq, int kv_col, int
     const int64_t n = blockIdx.x;
     const T* row = a + n * lda;
     float ss = 0.f;
-    for (int e = threadIdx.x; e < Rq; e += blockDim.x) {
-        const float v = to_float(row[e]);
-        ss = fmaf(v, v, ss);
+    if (blockIdx.y == 0) {             // the query latent; the other block of the token stores
+        for (int e = threadIdx.x; e < Rq; e += blockDim.x) {
+            const float v = to_float(row[e]);
+            ss = fmaf(v, v, ss);
+        }
+        ss = block_sum(ss, scratch);
+        const float q_inv = rsqrtf(ss / (float)Rq + eps);
+        for (int e = threadIdx.x; e < Rq; e += blockDim.x)
+            cq[n * Rq + e] = from_float<T>(to_float(row[e]) * q_inv * q_gain[e]);
+        return;
     }
-    ss = block_sum(ss, scratch);
-    const float q_inv = rsqrtf(ss / (float)Rq + eps);
-    for (int e = threadIdx.x; e < Rq; e += blockDim.x)
-        cq[n * Rq + e] = from_float<T>(to_float(row[e]) * q_inv * q_gain[e]);
     const int tr = token_row[n];
     if (!write || tr < 0) return;      // (uniform over the block)
     const int pos = positions[n];
@@ -172,6 +179,90 @@ __global__ void head_gate_kernel(T* __restrict__ x, int64_t ldx, const T* __rest
     }
 }
 
+// Steps of few tokens: out[n, h, j] = f(n, h) * sum_k x[n, h, k] * w[h, k, j], with w [H, K, J]
+// (the output index last, so that a warp reads a row of w at a time), for tiles of LS_T tokens
+// of one head: grid (H, ceil(N / LS_T)), 256 threads, the tile's x rows in shared memory as
+// 32-bit.  Threads are (k group, output): with fewer than 256 outputs the reduction is split
+// over 256 / roundup32(J) groups whose partial sums meet in shared memory in the order of the
+// groups, so a token's result depends on nothing else in the batch.  Options: `gate` (f = sigmoid
+// of gate[n * ldg + h], else 1), and a rotated tail as latent_q_rot_kernel writes it (the
+// head's entries K .. K + r of x, rotated, at out columns J .. J + tail, zeros behind the r).
+constexpr int LS_T = 8;
+template <typename T>
+__global__ void __launch_bounds__(256)
+latent_small_kernel(const T* __restrict__ x, int64_t ldx, int64_t hsx, const T* __restrict__ w,
+                    T* __restrict__ out, int64_t ldo, int64_t hso, int N, int K, int J,
+                    const T* __restrict__ gate, int64_t ldg, int r, int tail,
+                    const int* __restrict__ positions, const float* __restrict__ cos_t,
+                    const float* __restrict__ sin_t, int rot_dims) {
+    pdl_wait();
+    pdl_trigger();
+    extern __shared__ float ls_smem[];
+    const int h = blockIdx.x, n0 = blockIdx.y * LS_T, tid = threadIdx.x;
+    const int nt = min(LS_T, N - n0);
+    float* xs = ls_smem;                       // [LS_T][K]
+    float* red = ls_smem + LS_T * K;           // [groups][LS_T][JP]
+    for (int i = tid; i < LS_T * K; i += 256) {
+        const int t = i / K, k = i - t * K;
+        xs[i] = t < nt ? to_float(x[(int64_t)(n0 + t) * ldx + h * hsx + k]) : 0.f;
+    }
+    __syncthreads();
+    const int JP = J >= 256 ? 256 : ((J + 31) & ~31);
+    const int G = 256 / JP, g = tid / JP, jl = tid - g * JP;
+    const T* wh = w + (int64_t)h * K * J;
+    for (int j0 = 0; j0 < J; j0 += JP) {
+        const int j = j0 + jl;
+        float acc[LS_T];
+#pragma unroll
+        for (int t = 0; t < LS_T; ++t) acc[t] = 0.f;
+        if (g < G && j < J) {
+#pragma unroll 4
+            for (int k = g; k < K; k += G) {
+                const float wv = to_float(wh[(int64_t)k * J + j]);
+#pragma unroll
+                for (int t = 0; t < LS_T; ++t) acc[t] = fmaf(xs[t * K + k], wv, acc[t]);
+            }
+        }
+        if (G > 1) {
+            if (g < G) {
+#pragma unroll
+                for (int t = 0; t < LS_T; ++t) red[(g * LS_T + t) * JP + jl] = acc[t];
+            }
+            __syncthreads();
+            if (g == 0) {
+                for (int gg = 1; gg < G; ++gg)
+#pragma unroll
+                    for (int t = 0; t < LS_T; ++t) acc[t] += red[(gg * LS_T + t) * JP + jl];
+            }
+        }
+        if (g == 0 && j < J) {
+            for (int t = 0; t < nt; ++t) {
+                float f = 1.f;
+                if (gate) f = 1.0f / (1.0f + expf(-to_float(gate[(int64_t)(n0 + t) * ldg + h])));
+                out[(int64_t)(n0 + t) * ldo + h * hso + j] = from_float<T>(acc[t] * f);
+            }
+        }
+        if (G > 1) __syncthreads();
+    }
+    if (tail <= 0) return;
+    const int half = rot_dims / 2;
+    for (int idx = tid; idx < nt * tail; idx += 256) {
+        const int t = idx / tail, e = idx - t * tail;
+        const int pos = positions[n0 + t];
+        const T* qr = x + (int64_t)(n0 + t) * ldx + h * hsx + K;
+        float v = 0.f;
+        if (e < rot_dims) {
+            const int i = e < half ? e : e - half;
+            const float c = cos_t[(int64_t)pos * half + i], sn = sin_t[(int64_t)pos * half + i];
+            const float u = to_float(qr[i]), ww = to_float(qr[i + half]);
+            v = e < half ? u * c - ww * sn : ww * c + u * sn;
+        } else if (e < r) {
+            v = to_float(qr[e]);
+        }
+        out[(int64_t)(n0 + t) * ldo + h * hso + J + e] = from_float<T>(v);
+    }
+}
+
 }  // namespace sllm
 
 using namespace sllm;
@@ -189,12 +280,12 @@ SLLM_EXPORT int sllm_latent_prep(const void* a, int64_t lda, int Rq, int kv_col,
         return (int)cudaErrorInvalidValue;
     typedef __nv_bfloat16 bf16;
     if (dtype == 0)
-        return (int)sllm_launch_pdl(latent_prep_kernel<float>, dim3(n_tokens), dim3(256), 0, stream,
+        return (int)sllm_launch_pdl(latent_prep_kernel<float>, dim3(n_tokens, 2), dim3(256), 0, stream,
                                     (const float*)a, lda, Rq, kv_col, R, r, q_gain, kv_gain, eps,
                                     positions, token_row, cos_t, sin_t, rot_dims, (float*)cq,
                                     (float*)pages, block_table, table_stride, page_size, Dp, write);
     if (dtype == 1)
-        return (int)sllm_launch_pdl(latent_prep_kernel<bf16>, dim3(n_tokens), dim3(256), 0, stream,
+        return (int)sllm_launch_pdl(latent_prep_kernel<bf16>, dim3(n_tokens, 2), dim3(256), 0, stream,
                                     (const bf16*)a, lda, Rq, kv_col, R, r, q_gain, kv_gain, eps,
                                     positions, token_row, cos_t, sin_t, rot_dims, (bf16*)cq,
                                     (bf16*)pages, block_table, table_stride, page_size, Dp, write);
@@ -252,5 +343,34 @@ SLLM_EXPORT int sllm_head_gate(void* x, int64_t ldx, const void* gate, int64_t l
     if (dtype == 1)
         return (int)sllm_launch_pdl(head_gate_kernel<bf16>, dim3(n_tokens), dim3(256), 0, stream,
                                     (bf16*)x, ldx, (const bf16*)gate, ldg, H, V);
+    return (int)cudaErrorInvalidValue;
+}
+
+// Steps of few tokens (see latent_small_kernel).  gate may be null; tail 0 leaves the rotated
+// part out (then r, positions and the tables are unused).
+SLLM_EXPORT int sllm_latent_small(const void* x, int64_t ldx, int64_t hsx, const void* w, void* out,
+                                  int64_t ldo, int64_t hso, int n_tokens, int H, int K, int J,
+                                  const void* gate, int64_t ldg, int r, int tail,
+                                  const int* positions, const float* cos_t, const float* sin_t,
+                                  int rot_dims, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (H < 1 || H > 65535 || K < 1 || J < 1 || r < 0 || tail < 0 || (tail && tail < r) ||
+        rot_dims < 0 || (rot_dims & 1) || rot_dims > r || (n_tokens + LS_T - 1) / LS_T > 65535)
+        return (int)cudaErrorInvalidValue;
+    const int JP = J >= 256 ? 256 : ((J + 31) & ~31);
+    const size_t smem = sizeof(float) * ((size_t)LS_T * K + (size_t)(256 / JP) * LS_T * JP);
+    if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    dim3 grid(H, (n_tokens + LS_T - 1) / LS_T);
+    typedef __nv_bfloat16 bf16;
+    if (dtype == 0)
+        return (int)sllm_launch_pdl(latent_small_kernel<float>, grid, dim3(256), smem, stream,
+                                    (const float*)x, ldx, hsx, (const float*)w, (float*)out, ldo,
+                                    hso, n_tokens, K, J, (const float*)gate, ldg, r, tail,
+                                    positions, cos_t, sin_t, rot_dims);
+    if (dtype == 1)
+        return (int)sllm_launch_pdl(latent_small_kernel<bf16>, grid, dim3(256), smem, stream,
+                                    (const bf16*)x, ldx, hsx, (const bf16*)w, (bf16*)out, ldo, hso,
+                                    n_tokens, K, J, (const bf16*)gate, ldg, r, tail, positions,
+                                    cos_t, sin_t, rot_dims);
     return (int)cudaErrorInvalidValue;
 }

@@ -90,7 +90,9 @@ __global__ void embed_positional_kernel(const int* __restrict__ ids, const int* 
 template <typename T>
 __global__ void add_normed_kernel(float* __restrict__ resid, const T* __restrict__ delta,
                                   const float* __restrict__ gain, float eps,
-                                  T* __restrict__ cast_out, int d) {
+                                  T* __restrict__ cast_out, int d,
+                                  const float* __restrict__ gain2, float eps2,
+                                  T* __restrict__ out2) {
     pdl_wait();
     pdl_trigger();
     __shared__ float scratch[33];
@@ -104,11 +106,19 @@ __global__ void add_normed_kernel(float* __restrict__ resid, const T* __restrict
     const float total = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(total / (float)d + eps);
     float* x = resid + n * d;
+    float ss2 = 0.f;
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         const float v = x[i] + to_float(dl[i]) * inv * gain[i];
         x[i] = v;
+        ss2 += v * v;
         if (cast_out) cast_out[n * d + i] = from_float<T>(v);
     }
+    if (!out2) return;
+    // the norm in front of the next branch, on the row as it now is (a thread reads back what
+    // it has written itself)
+    const float inv2 = 1.0f / sqrtf(block_sum(ss2, scratch) / (float)d + eps2);
+    for (int i = threadIdx.x; i < d; i += blockDim.x)
+        out2[n * d + i] = from_float<T>(x[i] * inv2 * gain2[i]);
 }
 
 // add_normed_kernel with 16-byte accesses (d a multiple of Vec<T>::N, rows 16-byte aligned).
@@ -117,7 +127,9 @@ __global__ void add_normed_kernel(float* __restrict__ resid, const T* __restrict
 template <typename T>
 __global__ void add_normed_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta,
                                       const float* __restrict__ gain, float eps,
-                                      T* __restrict__ cast_out, int d) {
+                                      T* __restrict__ cast_out, int d,
+                                      const float* __restrict__ gain2, float eps2,
+                                      T* __restrict__ out2) {
     pdl_wait();
     pdl_trigger();
     constexpr int N = Vec<T>::N;
@@ -138,6 +150,7 @@ __global__ void add_normed_vec_kernel(float* __restrict__ resid, const T* __rest
     const float total = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(total / (float)d + eps);
     float* x = resid + n * d;
+    float ss2 = 0.f;
     for (int i = threadIdx.x * N; i < d; i += blockDim.x * N) {
         float v[N], y[N];
         if (i == (int)threadIdx.x * N) {
@@ -156,7 +169,31 @@ __global__ void add_normed_vec_kernel(float* __restrict__ resid, const T* __rest
             y[q + 3] = r.w + v[q + 3] * inv * g.w;
             *reinterpret_cast<float4*>(x + i + q) = make_float4(y[q], y[q + 1], y[q + 2], y[q + 3]);
         }
+#pragma unroll
+        for (int w = 0; w < N; ++w) {
+            ss2 += y[w] * y[w];
+            if (i == (int)threadIdx.x * N) first[w] = y[w];
+        }
         if (cast_out) Vec<T>::store(cast_out + n * d + i, y);
+    }
+    if (!out2) return;
+    // the norm in front of the next branch, on the row as it now is (beyond its first pass a
+    // thread reads back what it has written itself)
+    const float inv2 = 1.0f / sqrtf(block_sum(ss2, scratch) / (float)d + eps2);
+    for (int i = threadIdx.x * N; i < d; i += blockDim.x * N) {
+        float y[N];
+#pragma unroll
+        for (int q = 0; q < N; q += 4) {
+            float4 r;
+            if (i == (int)threadIdx.x * N) r = make_float4(first[q], first[q + 1], first[q + 2], first[q + 3]);
+            else r = *reinterpret_cast<const float4*>(x + i + q);
+            const float4 g = *reinterpret_cast<const float4*>(gain2 + i + q);
+            y[q] = r.x * inv2 * g.x;
+            y[q + 1] = r.y * inv2 * g.y;
+            y[q + 2] = r.z * inv2 * g.z;
+            y[q + 3] = r.w * inv2 * g.w;
+        }
+        Vec<T>::store(out2 + n * d + i, y);
     }
 }
 
@@ -346,30 +383,36 @@ SLLM_EXPORT int sllm_embed_positional(const int* ids, const int* pending, const 
     return 0;
 }
 
+// gain2 / eps2 / out2 (or nulls): out2 = T(rmsnorm(resid as updated) * gain2), the norm in front of
+// the next branch, from the same pass.
 SLLM_EXPORT int sllm_add_normed(float* resid, const void* delta, const float* gain, float eps,
-                                void* cast_out, int n_tokens, int d, int dtype,
-                                cudaStream_t stream) {
+                                void* cast_out, const float* gain2, float eps2, void* out2,
+                                int n_tokens, int d, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (d <= 0) return (int)cudaErrorInvalidValue;
+    if (d <= 0 || (out2 && !gain2)) return (int)cudaErrorInvalidValue;
     const int vec = dtype == 0 ? 4 : 8;
     const bool aligned = !(((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)gain |
-                            (uintptr_t)cast_out) & 15);
+                            (uintptr_t)cast_out | (uintptr_t)gain2 | (uintptr_t)out2) & 15);
     if (d % vec == 0 && aligned && dtype >= 0 && dtype <= 1) {
         int vt = 32;
         while (vt < 512 && vt * vec < d) vt <<= 1;
         SLLM_BY_DTYPE(dtype,
             (add_normed_vec_kernel<float><<<n_tokens, vt, 0, stream>>>(
-                resid, (const float*)delta, gain, eps, (float*)cast_out, d)),
+                resid, (const float*)delta, gain, eps, (float*)cast_out, d, gain2, eps2,
+                (float*)out2)),
             (add_normed_vec_kernel<__nv_bfloat16><<<n_tokens, vt, 0, stream>>>(
-                resid, (const __nv_bfloat16*)delta, gain, eps, (__nv_bfloat16*)cast_out, d)));
+                resid, (const __nv_bfloat16*)delta, gain, eps, (__nv_bfloat16*)cast_out, d, gain2,
+                eps2, (__nv_bfloat16*)out2)));
         return 0;
     }
     const int threads = row_threads(d);
     SLLM_BY_DTYPE(dtype,
         (add_normed_kernel<float><<<n_tokens, threads, 0, stream>>>(
-            resid, (const float*)delta, gain, eps, (float*)cast_out, d)),
+            resid, (const float*)delta, gain, eps, (float*)cast_out, d, gain2, eps2,
+            (float*)out2)),
         (add_normed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
-            resid, (const __nv_bfloat16*)delta, gain, eps, (__nv_bfloat16*)cast_out, d)));
+            resid, (const __nv_bfloat16*)delta, gain, eps, (__nv_bfloat16*)cast_out, d, gain2,
+            eps2, (__nv_bfloat16*)out2)));
     return 0;
 }
 

@@ -966,9 +966,12 @@ def embed_positional(ids: torch.Tensor, positions: torch.Tensor, table: torch.Te
 
 
 def add_normed(resid: torch.Tensor, delta: torch.Tensor, gain: torch.Tensor, eps: float,
-               cast_out: torch.Tensor | None = None) -> None:
+               cast_out: torch.Tensor | None = None,
+               then: tuple[torch.Tensor, float, torch.Tensor] | None = None) -> None:
     """resid += delta / sqrt(mean(delta^2) + eps) * gain, row by row, in 32-bit; ``cast_out``
-    (the dtype of ``delta``) gets the updated rows rounded."""
+    (the dtype of ``delta``) gets the updated rows rounded.  ``then = (gain2, eps2, out2)``:
+    ``out2`` (the dtype of ``delta``) gets the RMS norm of the updated rows with ``gain2``, the
+    norm in front of the next branch, from the same pass."""
     _need(resid, torch.float32, "resid")
     _need(delta, None, "delta")
     _need(gain, torch.float32, "gain")
@@ -979,9 +982,16 @@ def add_normed(resid: torch.Tensor, delta: torch.Tensor, gain: torch.Tensor, eps
         _need(cast_out, delta.dtype, "cast_out")
         if cast_out.shape != (n, d):
             raise KernelError("cast_out shape")
+    gain2, eps2, out2 = then if then is not None else (None, 0.0, None)
+    if then is not None:
+        _need(gain2, torch.float32, "gain2")
+        _need(out2, delta.dtype, "out2")
+        if gain2.numel() != d or out2.shape != (n, d):
+            raise KernelError("add_normed: the next norm's shapes")
     _check(_core("sllm_stream_ops").sllm_add_normed(
-        _ptr(resid), _ptr(delta), _ptr(gain), c_float(eps), _ptr(cast_out), c_int(n), c_int(d),
-        c_int(_code(delta.dtype)), _stream()), "add_normed")
+        _ptr(resid), _ptr(delta), _ptr(gain), c_float(eps), _ptr(cast_out), _ptr(gain2),
+        c_float(eps2), _ptr(out2), c_int(n), c_int(d), c_int(_code(delta.dtype)), _stream()),
+        "add_normed")
 
 
 def gated_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> torch.Tensor:
@@ -1614,6 +1624,62 @@ def head_gate(x: torch.Tensor, gate: torch.Tensor, n_heads: int) -> torch.Tensor
         _ptr(x), c_int64(x.stride(0)), _ptr(gate), c_int64(gate.stride(0)), c_int(n_heads),
         c_int(x.shape[1] // n_heads), c_int(n), c_int(_code(x.dtype)), _stream()), "head_gate")
     return x
+
+
+#: steps of up to this many tokens take :func:`latent_small` for a latent attention's products
+#: per head (beyond it the library's batched product wins)
+LATENT_SMALL_MAX_TOKENS = 64
+
+
+def latent_small_supports(k: int, j: int) -> bool:
+    """Whether :func:`latent_small` takes a reduction of ``k`` and ``j`` outputs per head (its
+    tile of tokens and its partial sums fit the default shared memory)."""
+    jp = 256 if j >= 256 else -(-j // 32) * 32
+    return k >= 1 and j >= 1 and 4 * (8 * k + (256 // jp) * 8 * jp) <= 48 * 1024
+
+
+def latent_small(x: torch.Tensor, x_head_stride: int, w: torch.Tensor, out: torch.Tensor,
+                 out_head_stride: int, gate: torch.Tensor | None = None,
+                 rot: tuple[int, torch.Tensor, torch.Tensor, torch.Tensor] | None = None
+                 ) -> torch.Tensor:
+    """A product per head for steps of few tokens, in one launch with what follows it:
+    ``out[n, h * out_head_stride + j] = f * sum_k x[n, h * x_head_stride + k] * w[h, k, j]`` for
+    ``w`` [H, K, J] (the output index last).  ``gate`` [N, H] (may be a column slice): ``f =
+    sigmoid(gate[n, h])``.  ``rot = (rot_dim, positions, cos, sin)``: the head's next ``rot_dim``
+    entries of ``x`` go behind the J outputs, the first ``2 * cos.shape[1]`` of them rotated by
+    the token's position (as :func:`latent_q_rot` does), zeros behind them up to
+    ``out_head_stride``."""
+    _need(x, None, "x", contiguous=False)
+    _need(w, x.dtype, "w")
+    _need(out, x.dtype, "out", contiguous=False)
+    h, k, j = w.shape
+    n = x.shape[0]
+    r = tail = rot_dims = 0
+    positions = cos = sin = None
+    if rot is not None:
+        r, positions, cos, sin = rot
+        _need(positions, torch.int32, "positions")
+        _need(cos, torch.float32, "cos")
+        _need(sin, torch.float32, "sin")
+        tail, rot_dims = out_head_stride - j, 2 * cos.shape[1]
+        if tail < r or rot_dims > r or sin.shape != cos.shape or x_head_stride < k + r:
+            raise KernelError("latent_small: the rotated part's shapes")
+    if gate is not None:
+        _need(gate, x.dtype, "gate", contiguous=False)
+        if gate.shape != (n, h) or gate.stride(1) != 1:
+            raise KernelError("latent_small: gate must be [tokens, heads]")
+    if x.stride(1) != 1 or out.stride(1) != 1 or out.shape[0] != n \
+            or (h - 1) * x_head_stride + k + r > x.shape[1] \
+            or (h - 1) * out_head_stride + j + tail > out.shape[1] \
+            or not latent_small_supports(k, j):
+        raise KernelError("latent_small shapes")
+    _check(_core("sllm_latent_attention").sllm_latent_small(
+        _ptr(x), c_int64(x.stride(0)), c_int64(x_head_stride), _ptr(w), _ptr(out),
+        c_int64(out.stride(0)), c_int64(out_head_stride), c_int(n), c_int(h), c_int(k), c_int(j),
+        _ptr(gate), c_int64(gate.stride(0) if gate is not None else 0), c_int(r), c_int(tail),
+        _ptr(positions), _ptr(cos), _ptr(sin), c_int(rot_dims), c_int(_code(x.dtype)), _stream()),
+        "latent_small")
+    return out
 
 
 def concat_cast(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> torch.Tensor:

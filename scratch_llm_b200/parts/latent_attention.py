@@ -61,7 +61,8 @@ class LatentAttention(Mixer):
         self.down: Linear | None = None     # [dq; dkv; g] in one product
         self.uq: Linear | None = None
         self.o: Linear | None = None
-        self.uk = self.uk_t = self.uv = self.q_gain = self.kv_gain = None
+        self.uk = self.uk_t = self.uv = self.uv_t = self.q_gain = self.kv_gain = None
+        self._small = False
 
     def kv_spec(self) -> KVSpec:
         return KVSpec(1, self.head_dim, None, planes=1)
@@ -107,6 +108,12 @@ class LatentAttention(Mixer):
         # [H, kv_rank, dim]: the absorb product's matrix with the reduction index last
         self.uk_t = self.uk.transpose(1, 2).contiguous()
         self.uv = put(tensors[n["uv"]]).view(H, self.value_dim, self.kv_rank).contiguous()
+        # [H, kv_rank, value_dim]: the value product's matrix with the output index last, for
+        # steps of few tokens (uk has that layout for the absorb product as it is)
+        self.uv_t = self.uv.transpose(1, 2).contiguous()
+        self._small = ctx.dtype == torch.bfloat16 \
+            and ops.latent_small_supports(self.dim, self.kv_rank) \
+            and ops.latent_small_supports(self.kv_rank, self.value_dim)
         self.q_gain, self.kv_gain = f32(tensors[n["dq_norm"]]), f32(tensors[n["dkv_norm"]])
 
     # ------------------------------------------------------------------------- forward
@@ -125,6 +132,18 @@ class LatentAttention(Mixer):
                         cache.block_table, cache.page_size, write)
         q = self.uq(cq)                                         # [N, H * (d + r)]
         qlat = torch.empty((n, H * Dp), dtype=q.dtype, device=q.device)
+        small = self._small and n <= ops.LATENT_SMALL_MAX_TOKENS
+        gate = a[:, self.q_rank + R + r:] if self.has_gate else None
+        if small:
+            # steps of few tokens: absorb product and rotation in one launch, value product and
+            # gate in another
+            ops.latent_small(q, d + r, self.uk, qlat, Dp, rot=(r, batch.positions, cos, sin))
+            olat = (torch.zeros if batch.padded else torch.empty)(
+                (n, H * Dp), dtype=q.dtype, device=q.device)
+            self._attend(qlat, olat, batch, cache)
+            o = torch.empty((n, H * V), dtype=q.dtype, device=q.device)
+            ops.latent_small(olat, Dp, self.uv_t, o, V, gate=gate)
+            return self.o(o)
         if q.dtype == torch.bfloat16:
             # the library's batched product, one batch per head, straight into its columns
             torch.bmm(q.view(n, H, d + r)[:, :, :d].transpose(0, 1), self.uk,
@@ -143,7 +162,7 @@ class LatentAttention(Mixer):
         else:
             ops.head_product(olat, Dp, self.uv, o, V)
         if self.has_gate:
-            ops.head_gate(o, a[:, self.q_rank + R + r:], H)
+            ops.head_gate(o, gate, H)
         return self.o(o)
 
     def _attend(self, q, out, batch, cache: CacheView) -> None:

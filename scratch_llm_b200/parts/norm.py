@@ -57,8 +57,19 @@ class RMSNorm(Norm):
         return ops.add_rmsnorm(resid, delta, self.weight, self.eps, out, out_rows)
 
     def add_normed(self, resid: torch.Tensor, delta: torch.Tensor,
-                   cast_out: torch.Tensor | None = None) -> None:
-        ops.add_normed(resid, delta, self.weight, self.eps, cast_out)
+                   cast_out: torch.Tensor | None = None, then: "RMSNorm | None" = None):
+        """``resid += rmsnorm(delta)``; with ``then`` (another norm of this kind and size) also
+        returns ``then(resid)`` from the same pass."""
+        if then is None:
+            ops.add_normed(resid, delta, self.weight, self.eps, cast_out)
+            return None
+        out = torch.empty_like(delta)
+        ops.add_normed(resid, delta, self.weight, self.eps, cast_out,
+                       (then.weight, then.eps, out))
+        return out
+
+    def chains_with(self, other) -> bool:
+        return isinstance(other, RMSNorm) and other.size == self.size
 
 
 @register_norm("dyt")

@@ -45,6 +45,13 @@ def test_norms_around_a_branch_with_gains_stored_around_zero(dtype, width):
     after.add_normed(resid, y.to(DEV))
     want = (x.double() + P.norm_around_zero(y.double(), wb.double(), eps)).float()
     torch.testing.assert_close(resid.cpu(), want, rtol=1e-5, atol=1e-5)   # the stream is 32-bit
+    # the norm on a branch's output and the norm in front of the next branch in one launch
+    r3 = x.clone().to(DEV)
+    assert after.chains_with(before) and not after.chains_with(RMSNorm(width + 1, eps, ""))
+    h = after.add_normed(r3, y.to(DEV), then=before)
+    assert torch.equal(r3, resid)
+    torch.testing.assert_close(h.float().cpu(), P.norm_around_zero(want.double(), wa.double(),
+                                                                   eps).float(), rtol=tol, atol=tol)
     # a gain of exactly -1 stored: the branch adds nothing
     zero = RMSNorm(width, eps, "", offset=1.0)
     zero.load({"": torch.full((width,), -1.0)}, ctx(dtype))
@@ -130,6 +137,48 @@ def test_products_and_gates_per_head(dtype):
     got = ops().head_gate(o.clone().to(DEV), wide.to(DEV)[:, 7:], H).float().cpu()
     want = o.double().view(n, H, V) * torch.sigmoid(wide[:, 7:].double())[..., None]
     torch.testing.assert_close(got, want.reshape(n, H * V).float(), rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n, H, K, J", [(8, 3, 16, 192), (13, 2, 192, 64), (1, 5, 21, 10),
+                                        (64, 1, 7, 300), (5, 4, 100, 96)])
+def test_products_per_head_of_steps_of_few_tokens(n, H, K, J, dtype):
+    """The kernel that steps of few tokens use instead of a batched product: alone, with the
+    gate, and with the rotated tail behind its outputs."""
+    from scratch_llm_b200.parts.position import Rotary
+    g = torch.Generator().manual_seed(n * K + J)
+    r, pad, base = 6, 3, 90.0
+    x = bf16_exact(torch.randn((n, H * (K + r)), generator=g))
+    w = bf16_exact(torch.randn((H, K, J), generator=g) * K ** -0.5)
+    gate = bf16_exact(torch.randn((n, 4 + H), generator=g))
+    want = torch.einsum("nhk,hkj->nhj", x.view(n, H, K + r)[..., :K].double(), w.double())
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    xd, wdev = x.to(DEV, dtype), w.to(DEV, dtype)
+    assert ops().latent_small_supports(K, J)
+    out = torch.full((n, H * J), float("nan"), dtype=dtype, device=DEV)
+    ops().latent_small(xd, K + r, wdev, out, J)
+    torch.testing.assert_close(out.view(n, H, J).float().cpu(), want.float(), rtol=tol, atol=tol)
+    gated = torch.full((n, H * J), float("nan"), dtype=dtype, device=DEV)
+    ops().latent_small(xd, K + r, wdev, gated, J, gate=gate.to(DEV, dtype)[:, 4:])
+    torch.testing.assert_close(
+        gated.view(n, H, J).float().cpu(),
+        (want * torch.sigmoid(gate[:, 4:].double())[..., None]).float(), rtol=tol, atol=tol)
+    pos = Rotary(r, base, 64, interleaved=False, rot_dims=4)
+    pos.load({}, ctx(torch.float32))
+    positions = [(7 * i) % 60 for i in range(n)]
+    tailed = torch.full((n, H * (J + r + pad)), float("nan"), dtype=dtype, device=DEV)
+    ops().latent_small(xd, K + r, wdev, tailed, J + r + pad, rot=(r, i32(positions), pos.cos,
+                                                                  pos.sin))
+    got = tailed.view(n, H, J + r + pad).float().cpu()
+    assert torch.equal(got[..., :J], out.view(n, H, J).float().cpu())
+    turned = P.rotate_split_half(x.double().view(n, H, K + r)[..., K:], torch.tensor(positions), 4,
+                                 base)
+    torch.testing.assert_close(got[..., J:J + r], turned.float(), rtol=tol, atol=tol)
+    assert torch.equal(got[..., J + r:], torch.zeros(n, H, pad))
+    # a token alone gets what it got in the batch, bit for bit
+    alone = torch.empty((1, H * J), dtype=dtype, device=DEV)
+    ops().latent_small(xd[n - 1:], K + r, wdev, alone, J)
+    assert torch.equal(alone[0], out[n - 1])
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
