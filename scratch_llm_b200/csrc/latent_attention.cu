@@ -51,7 +51,7 @@ latent_prep_kernel(const T* __restrict__ a, int64_t lda, int Rq, int kv_col, int
             ss = fmaf(v, v, ss);
         }
         ss = block_sum(ss, scratch);
-        const float q_inv = rsqrtf(ss / (float)Rq + eps);
+        const float q_inv = 1.0f / sqrtf(ss / (float)Rq + eps);
         for (int e = threadIdx.x; e < Rq; e += blockDim.x)
             cq[n * Rq + e] = from_float<T>(to_float(row[e]) * q_inv * q_gain[e]);
         return;
@@ -69,7 +69,7 @@ latent_prep_kernel(const T* __restrict__ a, int64_t lda, int Rq, int kv_col, int
         ss = fmaf(v, v, ss);
     }
     ss = block_sum(ss, scratch);
-    const float kv_inv = rsqrtf(ss / (float)R + eps);
+    const float kv_inv = 1.0f / sqrtf(ss / (float)R + eps);
     for (int e = threadIdx.x; e < R; e += blockDim.x)
         dst[e] = from_float<T>(to_float(kv[e]) * kv_inv * kv_gain[e]);
     const int half = rot_dims / 2;
@@ -180,14 +180,20 @@ __global__ void head_gate_kernel(T* __restrict__ x, int64_t ldx, const T* __rest
 }
 
 // Steps of few tokens: out[n, h, j] = f(n, h) * sum_k x[n, h, k] * w[h, k, j], with w [H, K, J]
-// (the output index last, so that a warp reads a row of w at a time), for tiles of LS_T tokens
-// of one head: grid (H, ceil(N / LS_T)), 256 threads, the tile's x rows in shared memory as
-// 32-bit.  Threads are (k group, output): with fewer than 256 outputs the reduction is split
-// over 256 / roundup32(J) groups whose partial sums meet in shared memory in the order of the
-// groups, so a token's result depends on nothing else in the batch.  Options: `gate` (f = sigmoid
-// of gate[n * ldg + h], else 1), and a rotated tail as latent_q_rot_kernel writes it (the
-// head's entries K .. K + r of x, rotated, at out columns J .. J + tail, zeros behind the r).
+// (the output index last, so that a warp reads a row of w at a time).  A CTA has LS_T tokens of
+// one head and LS_J neighbouring outputs: grid (H, ceil(N / LS_T), ceil(J / LS_J)), 256 threads,
+// the tile's x rows in shared memory as 32-bit.  Warp g takes the reduction indices g, g + 8, ...
+// (a lane is an output) and requests eight rows of w at a time; the eight partial sums of an
+// output meet in shared memory and are added in the order of the warps, so a token's result
+// depends on nothing else in the batch.  The matrices of a step are small (H K J entries), so
+// what counts is that enough CTAs have enough loads in flight.  Options: `gate` (f = sigmoid of
+// gate[n * ldg + h], else 1), and a rotated tail as latent_q_rot_kernel writes it (the head's
+// entries K .. K + r of x, rotated, at out columns J .. J + tail, zeros behind the r), which the
+// CTAs of the first outputs write.
 constexpr int LS_T = 8;
+constexpr int LS_J = 32;
+constexpr int LS_G = 8;
+static_assert(LS_G == LS_T && LS_G * 32 == 256 && LS_J == 32, "a warp per reduction group and per token");
 template <typename T>
 __global__ void __launch_bounds__(256)
 latent_small_kernel(const T* __restrict__ x, int64_t ldx, int64_t hsx, const T* __restrict__ w,
@@ -195,56 +201,64 @@ latent_small_kernel(const T* __restrict__ x, int64_t ldx, int64_t hsx, const T* 
                     const T* __restrict__ gate, int64_t ldg, int r, int tail,
                     const int* __restrict__ positions, const float* __restrict__ cos_t,
                     const float* __restrict__ sin_t, int rot_dims) {
-    pdl_wait();
-    pdl_trigger();
     extern __shared__ float ls_smem[];
     const int h = blockIdx.x, n0 = blockIdx.y * LS_T, tid = threadIdx.x;
+    const int g = tid >> 5, lane = tid & 31;
+    const int j = blockIdx.z * LS_J + lane;
     const int nt = min(LS_T, N - n0);
     float* xs = ls_smem;                       // [LS_T][K]
-    float* red = ls_smem + LS_T * K;           // [groups][LS_T][JP]
+    float* red = ls_smem + LS_T * K;           // [LS_G][LS_T][LS_J]
+    // the matrix does not depend on the kernel before: its first rows are requested ahead of it
+    const T* wj = w + (int64_t)h * K * J + (j < J ? j : 0);
+    T wv[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int k = g + u * LS_G;
+        wv[u] = k < K ? wj[(int64_t)k * J] : from_float<T>(0.f);
+    }
+    pdl_wait();
+    pdl_trigger();
     for (int i = tid; i < LS_T * K; i += 256) {
         const int t = i / K, k = i - t * K;
         xs[i] = t < nt ? to_float(x[(int64_t)(n0 + t) * ldx + h * hsx + k]) : 0.f;
     }
     __syncthreads();
-    const int JP = J >= 256 ? 256 : ((J + 31) & ~31);
-    const int G = 256 / JP, g = tid / JP, jl = tid - g * JP;
-    const T* wh = w + (int64_t)h * K * J;
-    for (int j0 = 0; j0 < J; j0 += JP) {
-        const int j = j0 + jl;
-        float acc[LS_T];
+    float acc[LS_T];
 #pragma unroll
-        for (int t = 0; t < LS_T; ++t) acc[t] = 0.f;
-        if (g < G && j < J) {
-#pragma unroll 4
-            for (int k = g; k < K; k += G) {
-                const float wv = to_float(wh[(int64_t)k * J + j]);
+    for (int t = 0; t < LS_T; ++t) acc[t] = 0.f;
+    for (int k0 = g; k0 < K; k0 += 8 * LS_G) {
+        T nx[8];
 #pragma unroll
-                for (int t = 0; t < LS_T; ++t) acc[t] = fmaf(xs[t * K + k], wv, acc[t]);
-            }
+        for (int u = 0; u < 8; ++u) {           // the next eight rows, before these are used
+            const int k = k0 + (8 + u) * LS_G;
+            nx[u] = k < K ? wj[(int64_t)k * J] : from_float<T>(0.f);
         }
-        if (G > 1) {
-            if (g < G) {
 #pragma unroll
-                for (int t = 0; t < LS_T; ++t) red[(g * LS_T + t) * JP + jl] = acc[t];
-            }
-            __syncthreads();
-            if (g == 0) {
-                for (int gg = 1; gg < G; ++gg)
+        for (int u = 0; u < 8; ++u) {
+            const int k = k0 + u * LS_G;
+            if (k < K) {
+                const float wf = to_float(wv[u]);
 #pragma unroll
-                    for (int t = 0; t < LS_T; ++t) acc[t] += red[(gg * LS_T + t) * JP + jl];
+                for (int t = 0; t < LS_T; ++t) acc[t] = fmaf(xs[t * K + k], wf, acc[t]);
             }
+            wv[u] = nx[u];
         }
-        if (g == 0 && j < J) {
-            for (int t = 0; t < nt; ++t) {
-                float f = 1.f;
-                if (gate) f = 1.0f / (1.0f + expf(-to_float(gate[(int64_t)(n0 + t) * ldg + h])));
-                out[(int64_t)(n0 + t) * ldo + h * hso + j] = from_float<T>(acc[t] * f);
-            }
-        }
-        if (G > 1) __syncthreads();
     }
-    if (tail <= 0) return;
+#pragma unroll
+    for (int t = 0; t < LS_T; ++t) red[(g * LS_T + t) * LS_J + lane] = acc[t];
+    __syncthreads();
+    {   // thread (token g, output lane): the partial sums in the order of the warps
+        const int t = g;
+        float sum = red[t * LS_J + lane];
+#pragma unroll
+        for (int gg = 1; gg < LS_G; ++gg) sum += red[(gg * LS_T + t) * LS_J + lane];
+        if (t < nt && j < J) {
+            float f = 1.f;
+            if (gate) f = 1.0f / (1.0f + expf(-to_float(gate[(int64_t)(n0 + t) * ldg + h])));
+            out[(int64_t)(n0 + t) * ldo + h * hso + j] = from_float<T>(sum * f);
+        }
+    }
+    if (tail <= 0 || blockIdx.z != 0) return;
     const int half = rot_dims / 2;
     for (int idx = tid; idx < nt * tail; idx += 256) {
         const int t = idx / tail, e = idx - t * tail;
@@ -357,10 +371,9 @@ SLLM_EXPORT int sllm_latent_small(const void* x, int64_t ldx, int64_t hsx, const
     if (H < 1 || H > 65535 || K < 1 || J < 1 || r < 0 || tail < 0 || (tail && tail < r) ||
         rot_dims < 0 || (rot_dims & 1) || rot_dims > r || (n_tokens + LS_T - 1) / LS_T > 65535)
         return (int)cudaErrorInvalidValue;
-    const int JP = J >= 256 ? 256 : ((J + 31) & ~31);
-    const size_t smem = sizeof(float) * ((size_t)LS_T * K + (size_t)(256 / JP) * LS_T * JP);
-    if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
-    dim3 grid(H, (n_tokens + LS_T - 1) / LS_T);
+    const size_t smem = sizeof(float) * ((size_t)LS_T * K + (size_t)LS_G * LS_T * LS_J);
+    if (smem > 48 * 1024 || (J + LS_J - 1) / LS_J > 65535) return (int)cudaErrorInvalidValue;
+    dim3 grid(H, (n_tokens + LS_T - 1) / LS_T, (J + LS_J - 1) / LS_J);
     typedef __nv_bfloat16 bf16;
     if (dtype == 0)
         return (int)sllm_launch_pdl(latent_small_kernel<float>, grid, dim3(256), smem, stream,

@@ -1634,8 +1634,7 @@ LATENT_SMALL_MAX_TOKENS = 64
 def latent_small_supports(k: int, j: int) -> bool:
     """Whether :func:`latent_small` takes a reduction of ``k`` and ``j`` outputs per head (its
     tile of tokens and its partial sums fit the default shared memory)."""
-    jp = 256 if j >= 256 else -(-j // 32) * 32
-    return k >= 1 and j >= 1 and 4 * (8 * k + (256 // jp) * 8 * jp) <= 48 * 1024
+    return k >= 1 and 1 <= j <= 32 * 65535 and 4 * (8 * k + 8 * 8 * 32) <= 48 * 1024
 
 
 def latent_small(x: torch.Tensor, x_head_stride: int, w: torch.Tensor, out: torch.Tensor,
