@@ -38,13 +38,47 @@ latent_prep_kernel(const T* __restrict__ a, int64_t lda, int Rq, int kv_col, int
                    const int* __restrict__ positions, const int* __restrict__ token_row,
                    const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot_dims,
                    T* __restrict__ cq, T* __restrict__ pages, const int* __restrict__ block_table,
-                   int table_stride, int page_size, int Dp, int write) {
+                   int table_stride, int page_size, int Dp, int write, int vec) {
     pdl_wait();
     pdl_trigger();
     __shared__ float scratch[33];
     const int64_t n = blockIdx.x;
     const T* row = a + n * lda;
     float ss = 0.f;
+    if (blockIdx.y == 0 && vec) {      // the query latent with 16-byte accesses
+        constexpr int VN = Vec<T>::N;
+        float first[VN];               // a thread's first vector stays in registers
+        for (int e = threadIdx.x * VN; e < Rq; e += blockDim.x * VN) {
+            float v[VN];
+            Vec<T>::load(row + e, v);
+#pragma unroll
+            for (int k = 0; k < VN; ++k) {
+                ss = fmaf(v[k], v[k], ss);
+                if (e == (int)threadIdx.x * VN) first[k] = v[k];
+            }
+        }
+        ss = block_sum(ss, scratch);
+        const float q_inv = 1.0f / sqrtf(ss / (float)Rq + eps);
+        for (int e = threadIdx.x * VN; e < Rq; e += blockDim.x * VN) {
+            float v[VN];
+            if (e == (int)threadIdx.x * VN) {
+#pragma unroll
+                for (int k = 0; k < VN; ++k) v[k] = first[k];
+            } else {
+                Vec<T>::load(row + e, v);
+            }
+#pragma unroll
+            for (int k = 0; k < VN; k += 4) {
+                const float4 g = *reinterpret_cast<const float4*>(q_gain + e + k);
+                v[k] *= q_inv * g.x;
+                v[k + 1] *= q_inv * g.y;
+                v[k + 2] *= q_inv * g.z;
+                v[k + 3] *= q_inv * g.w;
+            }
+            Vec<T>::store(cq + n * Rq + e, v);
+        }
+        return;
+    }
     if (blockIdx.y == 0) {             // the query latent; the other block of the token stores
         for (int e = threadIdx.x; e < Rq; e += blockDim.x) {
             const float v = to_float(row[e]);
@@ -179,6 +213,72 @@ __global__ void head_gate_kernel(T* __restrict__ x, int64_t ldx, const T* __rest
     }
 }
 
+// head_gate_kernel with 16-byte accesses (V a multiple of Vec<T>::N, rows 16-byte aligned):
+// a thread's vector lies within one head.  grid (N, ceil(H * V / (N * 256))).
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_gate_vec_kernel(T* __restrict__ x, int64_t ldx, const T* __restrict__ gate, int64_t ldg,
+                     int H, int V) {
+    pdl_wait();
+    pdl_trigger();
+    constexpr int VN = Vec<T>::N;
+    const int64_t n = blockIdx.x;
+    const int idx = (blockIdx.y * 256 + threadIdx.x) * VN;
+    if (idx >= H * V) return;
+    const float g = to_float(gate[n * ldg + idx / V]);
+    const float f = 1.0f / (1.0f + expf(-g));
+    float v[VN];
+    Vec<T>::load(x + n * ldx + idx, v);
+#pragma unroll
+    for (int i = 0; i < VN; ++i) v[i] *= f;
+    Vec<T>::store(x + n * ldx + idx, v);
+}
+
+// latent_q_rot_kernel with 16-byte accesses: d, r, R, the tail Dp - R and rot_dims / 2 are
+// multiples of Vec<T>::N and rows are 16-byte aligned, so a thread's vector of the tail is
+// wholly in the rotation's first half, its second half, the unrotated rest or the zeros.
+// grid (N, ceil(H * tail / (N * 256))).
+template <typename T>
+__global__ void __launch_bounds__(256)
+latent_q_rot_vec_kernel(const T* __restrict__ q, int64_t ldq, int H, int d, int r,
+                        const int* __restrict__ positions, const float* __restrict__ cos_t,
+                        const float* __restrict__ sin_t, int rot_dims, T* __restrict__ out,
+                        int64_t ldo, int R, int Dp) {
+    pdl_wait();
+    pdl_trigger();
+    constexpr int VN = Vec<T>::N;
+    const int64_t n = blockIdx.x;
+    const int tail = Dp - R, half = rot_dims / 2;
+    const int idx = (blockIdx.y * 256 + threadIdx.x) * VN;
+    if (idx >= H * tail) return;
+    const int h = idx / tail, e = idx - h * tail;
+    const T* qr = q + n * ldq + (int64_t)h * (d + r) + d;
+    float v[VN];
+    if (e < rot_dims) {
+        const int i = e < half ? e : e - half;
+        const int64_t at = (int64_t)positions[n] * half + i;
+        float u[VN], w[VN];
+        Vec<T>::load(qr + i, u);
+        Vec<T>::load(qr + i + half, w);
+#pragma unroll
+        for (int k = 0; k < VN; k += 4) {
+            const float4 c = *reinterpret_cast<const float4*>(cos_t + at + k);
+            const float4 sn = *reinterpret_cast<const float4*>(sin_t + at + k);
+            const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+            for (int m = 0; m < 4; ++m)
+                v[k + m] = e < half ? u[k + m] * cc[m] - w[k + m] * ss[m]
+                                    : w[k + m] * cc[m] + u[k + m] * ss[m];
+        }
+    } else if (e < r) {
+        Vec<T>::load(qr + e, v);
+    } else {
+#pragma unroll
+        for (int k = 0; k < VN; ++k) v[k] = 0.f;
+    }
+    Vec<T>::store(out + n * ldo + (int64_t)h * Dp + R + e, v);
+}
+
 // Steps of few tokens: out[n, h, j] = f(n, h) * sum_k x[n, h, k] * w[h, k, j], with w [H, K, J]
 // (the output index last, so that a warp reads a row of w at a time).  A CTA has LS_T tokens of
 // one head and LS_J neighbouring outputs: grid (H, ceil(N / LS_T), ceil(J / LS_J)), 256 threads,
@@ -293,16 +393,20 @@ SLLM_EXPORT int sllm_latent_prep(const void* a, int64_t lda, int Rq, int kv_col,
         Dp < R + r || page_size < 1 || kv_col < 0)
         return (int)cudaErrorInvalidValue;
     typedef __nv_bfloat16 bf16;
+    // the query latent moves 16 bytes at a time where its rows allow it
+    const int vn = dtype == 0 ? 4 : 8;
+    const int vec = Rq % vn == 0 && lda % vn == 0 &&
+                    !(((uintptr_t)a | (uintptr_t)cq | (uintptr_t)q_gain) & 15);
     if (dtype == 0)
         return (int)sllm_launch_pdl(latent_prep_kernel<float>, dim3(n_tokens, 2), dim3(256), 0, stream,
                                     (const float*)a, lda, Rq, kv_col, R, r, q_gain, kv_gain, eps,
                                     positions, token_row, cos_t, sin_t, rot_dims, (float*)cq,
-                                    (float*)pages, block_table, table_stride, page_size, Dp, write);
+                                    (float*)pages, block_table, table_stride, page_size, Dp, write, vec);
     if (dtype == 1)
         return (int)sllm_launch_pdl(latent_prep_kernel<bf16>, dim3(n_tokens, 2), dim3(256), 0, stream,
                                     (const bf16*)a, lda, Rq, kv_col, R, r, q_gain, kv_gain, eps,
                                     positions, token_row, cos_t, sin_t, rot_dims, (bf16*)cq,
-                                    (bf16*)pages, block_table, table_stride, page_size, Dp, write);
+                                    (bf16*)pages, block_table, table_stride, page_size, Dp, write, vec);
     return (int)cudaErrorInvalidValue;
 }
 
@@ -314,8 +418,21 @@ SLLM_EXPORT int sllm_latent_q_rot(const void* q, int64_t ldq, int H, int d, int 
     if (H < 1 || d < 0 || r < 0 || rot_dims < 0 || (rot_dims & 1) || rot_dims > r || Dp < R + r)
         return (int)cudaErrorInvalidValue;
     const int work = H * (Dp - R);
-    dim3 grid(n_tokens, (work + 255) / 256 > 8 ? 8 : (work + 255) / 256);
     typedef __nv_bfloat16 bf16;
+    const int vn = dtype == 0 ? 4 : 8;
+    if ((d | r | R | Dp | (rot_dims / 2)) % vn == 0 && ldq % vn == 0 && ldo % vn == 0 &&
+        !(((uintptr_t)q | (uintptr_t)out | (uintptr_t)cos_t | (uintptr_t)sin_t) & 15) &&
+        (work / vn + 255) / 256 <= 65535 && dtype >= 0 && dtype <= 1) {
+        dim3 vgrid(n_tokens, (work / vn + 255) / 256);
+        if (dtype == 0)
+            return (int)sllm_launch_pdl(latent_q_rot_vec_kernel<float>, vgrid, dim3(256), 0, stream,
+                                        (const float*)q, ldq, H, d, r, positions, cos_t, sin_t,
+                                        rot_dims, (float*)out, ldo, R, Dp);
+        return (int)sllm_launch_pdl(latent_q_rot_vec_kernel<bf16>, vgrid, dim3(256), 0, stream,
+                                    (const bf16*)q, ldq, H, d, r, positions, cos_t, sin_t,
+                                    rot_dims, (bf16*)out, ldo, R, Dp);
+    }
+    dim3 grid(n_tokens, (work + 255) / 256 > 8 ? 8 : (work + 255) / 256);
     if (dtype == 0)
         return (int)sllm_launch_pdl(latent_q_rot_kernel<float>, grid, dim3(256), 0, stream,
                                     (const float*)q, ldq, H, d, r, positions, cos_t, sin_t,
@@ -351,6 +468,16 @@ SLLM_EXPORT int sllm_head_gate(void* x, int64_t ldx, const void* gate, int64_t l
     if (n_tokens <= 0) return 0;
     if (H < 1 || V < 1) return (int)cudaErrorInvalidValue;
     typedef __nv_bfloat16 bf16;
+    const int vn = dtype == 0 ? 4 : 8;
+    if (V % vn == 0 && ldx % vn == 0 && !((uintptr_t)x & 15) && dtype >= 0 && dtype <= 1 &&
+        (H * V / vn + 255) / 256 <= 65535) {
+        dim3 vgrid(n_tokens, (H * V / vn + 255) / 256);
+        if (dtype == 0)
+            return (int)sllm_launch_pdl(head_gate_vec_kernel<float>, vgrid, dim3(256), 0, stream,
+                                        (float*)x, ldx, (const float*)gate, ldg, H, V);
+        return (int)sllm_launch_pdl(head_gate_vec_kernel<bf16>, vgrid, dim3(256), 0, stream,
+                                    (bf16*)x, ldx, (const bf16*)gate, ldg, H, V);
+    }
     if (dtype == 0)
         return (int)sllm_launch_pdl(head_gate_kernel<float>, dim3(n_tokens), dim3(256), 0, stream,
                                     (float*)x, ldx, (const float*)gate, ldg, H, V);

@@ -24,38 +24,6 @@ __device__ __forceinline__ float activate(float z, int act) {
     return act == 1 ? act_gelu_tanh(z) : act_silu(z);
 }
 
-// 16 bytes at a time: 4 floats or 8 bfloat16, as floats.
-template <typename T> struct Vec;
-template <> struct Vec<float> {
-    static constexpr int N = 4;
-    static __device__ __forceinline__ void load(const float* p, float* v) {
-        const float4 r = *reinterpret_cast<const float4*>(p);
-        v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
-    }
-    static __device__ __forceinline__ void store(float* p, const float* v) {
-        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
-    }
-};
-template <> struct Vec<__nv_bfloat16> {
-    static constexpr int N = 8;
-    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
-        const uint4 r = *reinterpret_cast<const uint4*>(p);
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            v[2 * i] = __low2float(h[i]);
-            v[2 * i + 1] = __high2float(h[i]);
-        }
-    }
-    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) {
-        uint4 r;
-        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-        *reinterpret_cast<uint4*>(p) = r;
-    }
-};
-
 // out[n, e] = table[ids[n], e] * scale + pe(positions[n], e), where, with inv_freq != nullptr,
 // pe(p, 2i) = sin(p * inv_freq[i]) and pe(p, 2i + 1) = cos(p * inv_freq[i]) (angles in 32-bit),
 // else 0.  cast_out (may be null) gets the same row rounded to T.  An id -1 - j stands for

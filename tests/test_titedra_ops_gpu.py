@@ -63,13 +63,17 @@ def test_norms_around_a_branch_with_gains_stored_around_zero(dtype, width):
 # -------------------------------------------------------------- the latent attention's steps
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("Rq, R, r, rot, page", [(20, 24, 8, 8, 4), (16, 21, 6, 4, 8),
-                                                 (8, 36, 28, 28, 16), (64, 96, 32, 32, 16),
-                                                 (5, 3, 2, 2, 4)])
-def test_latents_are_normed_rotated_and_stored_as_one_vector(Rq, R, r, rot, page, dtype):
+@pytest.mark.parametrize("Rq, R, r, rot, page, extra, d", [
+    (20, 24, 8, 8, 4, 3, 5), (16, 21, 6, 4, 8, 3, 5), (8, 36, 28, 28, 16, 3, 5),
+    (64, 96, 32, 32, 16, 3, 5), (5, 3, 2, 2, 4, 3, 5),
+    # rows that move 16 bytes at a time: every size a multiple of 8, a query latent of more
+    # than one vector a thread, a rotated part with an unrotated rest and zeros behind it
+    (64, 96, 32, 32, 16, 0, 8), (2304, 48, 16, 16, 8, 8, 16), (24, 32, 24, 16, 4, 0, 8)])
+def test_latents_are_normed_rotated_and_stored_as_one_vector(Rq, R, r, rot, page, extra, d,
+                                                             dtype):
     """The kernel behind the down projections: the query latent's norm, the cached vector
     [normed latent | rotated shared key part | zeros] at the token's page place; tokens of
-    padding rows store nothing."""
+    padding rows store nothing.  ``extra``: gate columns behind, a wider buffer."""
     from scratch_llm_b200.parts.position import Rotary
     g = torch.Generator().manual_seed(R)
     base, eps, n = 300.0, 1e-4, 6
@@ -77,7 +81,6 @@ def test_latents_are_normed_rotated_and_stored_as_one_vector(Rq, R, r, rot, page
     pos.load({}, ctx(torch.float32))
     assert pos.cos.shape == (64, rot // 2)
     Dp = -(-(R + r) // 16) * 16
-    extra = 3                                        # gate columns behind: a wider buffer
     a = (torch.randn((n, Rq + R + r + extra), generator=g) * 2).to(dtype)
     gq, gkv = torch.randn((Rq,), generator=g), torch.randn((R,), generator=g)
     positions = [0, 1, 2, 3, 41, 7]
@@ -101,7 +104,7 @@ def test_latents_are_normed_rotated_and_stored_as_one_vector(Rq, R, r, rot, page
     p = positions[-1]
     assert pages[int(table[0, p // page]), 0, 0, p % page].isnan().all()
     # the queries' rotated parts land behind the absorbed part of each head
-    H, d = 3, 5
+    H = 3
     q = (torch.randn((n, H * (d + r)), generator=g)).to(dtype)
     out = torch.full((n, H * Dp), float("nan"), dtype=dtype, device=DEV)
     ops().latent_q_rot(q.to(DEV), H, d, r, i32(positions), pos.cos, pos.sin, out, R)
@@ -130,13 +133,14 @@ def test_products_and_gates_per_head(dtype):
     alone = torch.zeros((1, H * (J + 2)), dtype=dtype, device=DEV)
     ops().head_product(x[17:18].to(DEV, dtype), K + 4, w.to(DEV, dtype), alone, J + 2)
     assert torch.equal(alone[0], out[17])
-    # one gate per head, read from a slice of a wider buffer
-    V = 10
-    o = torch.randn((n, H * V), generator=g).to(dtype)
-    wide = torch.randn((n, 7 + H), generator=g).to(dtype)
-    got = ops().head_gate(o.clone().to(DEV), wide.to(DEV)[:, 7:], H).float().cpu()
-    want = o.double().view(n, H, V) * torch.sigmoid(wide[:, 7:].double())[..., None]
-    torch.testing.assert_close(got, want.reshape(n, H * V).float(), rtol=tol, atol=tol)
+    # one gate per head, read from a slice of a wider buffer (16: rows that move 16 bytes at a
+    # time)
+    for V in (10, 16):
+        o = torch.randn((n, H * V), generator=g).to(dtype)
+        wide = torch.randn((n, 7 + H), generator=g).to(dtype)
+        got = ops().head_gate(o.clone().to(DEV), wide.to(DEV)[:, 7:], H).float().cpu()
+        want = o.double().view(n, H, V) * torch.sigmoid(wide[:, 7:].double())[..., None]
+        torch.testing.assert_close(got, want.reshape(n, H * V).float(), rtol=tol, atol=tol)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
