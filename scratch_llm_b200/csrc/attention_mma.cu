@@ -135,10 +135,10 @@ struct AttnArgs {
     // to the new key and to the new value first (projections with biases); rot (0 = HD): only the
     // first rot entries of a head turn (tables of rot / 2 columns), the rest pass unchanged.
     const float* rope_bias = nullptr; int rot = 0;
-    // attn_decode_cs_kernel with several splits, one query tile per row: a counter per (listed
-    // row, kv head), zero between launches.  The CTA that finishes last for a row and kv head
-    // (it sees the count n_splits - 1) merges the splits' partial results itself, so that no
-    // merge kernel follows; nobody waits for anybody.  nullptr: a merge kernel follows.
+    // attn_decode_cs_kernel with several splits, rows of one new token: a counter per (listed
+    // row, kv head, tile of 16 query heads), zero between launches.  The CTA that finishes last
+    // for a tile (it sees the count n_splits - 1) merges the splits' partial results itself, so
+    // that no merge kernel follows; nobody waits for anybody.  nullptr: a merge kernel follows.
     int* merge_count;
 };
 
@@ -875,15 +875,18 @@ __global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnAr
         __threadfence();
         __syncthreads();
         if (tid == 0) {
-            int* count = a.merge_count + (size_t)blockIdx.y * a.G + g;
+            int* count = a.merge_count +
+                         ((size_t)blockIdx.y * a.G + g) * (gridDim.x / n_splits) + q_tile;
             is_last = atomicAdd(count, 1) == n_splits - 1;
             if (is_last) *count = 0;                 // zero again for the next launch
         }
         __syncthreads();
         if (!is_last) return;
         __threadfence();
-        for (int idx = tid; idx < n_packed * (HD / 4); idx += THREADS) {
-            const int p = idx / (HD / 4), d = (idx - p * (HD / 4)) * 4;
+        const int n_here = min(M::BQ, n_packed - q0);   // this tile's packed queries
+        for (int idx = tid; idx < n_here * (HD / 4); idx += THREADS) {
+            const int pi = idx / (HD / 4), d = (idx - pi * (HD / 4)) * 4;
+            const int p = q0 + pi;
             const int tok = p / GS, j = p - tok * GS;
             if (t0 + tok >= a.part_tokens) continue;
             const int64_t qh = (int64_t)(t0 + tok) * a.H + g * GS + j;
@@ -1080,9 +1083,10 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
     if (e != cudaSuccess) return (int)e;
     dim3 grid((((int64_t)max_new * GS + 15) / 16) * n_splits, n_list, G);
 #if SLLM_HEAD_DIM % 64 == 0
-    // rows of one new token with one tile of queries each: the last CTA to finish for a row and
-    // kv head may merge the splits itself (merge_count: n_list * G counters, zero between launches)
-    if (n_splits > 1 && merge_count != nullptr && max_new == 1 && GS <= 16)
+    // rows of one new token: the last CTA to finish for a row, kv head and tile of 16 query
+    // heads may merge the splits itself (merge_count: n_list * G * ceil(GS / 16) counters, zero
+    // between launches)
+    if (n_splits > 1 && merge_count != nullptr && max_new == 1)
         a.merge_count = merge_count;
     e = cudaFuncSetAttribute(attn_decode_cs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem);

@@ -623,7 +623,7 @@ def attention_mma(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tenso
     ``slopes`` / ``sinks`` as in :func:`attention_simt`.  ``gate`` [N, H * hd] (may be a column
     slice): every output is multiplied by ``sigmoid(gate)`` before it is stored.
     ``merge_inside`` (split rows of one token, head sizes that are multiples of 64): the CTA that
-    finishes last for a row and kv head merges the splits, no merge kernel follows (launches
+    finishes last for a row, kv head and tile of 16 query heads merges the splits, no merge kernel follows (launches
     share the counters per device and must be ordered by their stream)."""
     _head_vectors(slopes, sinks, n_heads)
     if gate is not None:
@@ -655,7 +655,8 @@ def attention_mma(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tenso
             raise KernelError(f"scratch holds {scratch.numel()} floats, {need} are needed")
     counters = None
     if merge_inside and split and n_splits > 1 and max_new == 1 and head_dim % 64 == 0:
-        counters = _merge_counter(q.device, n_list * n_kv_heads)
+        counters = _merge_counter(q.device,
+                                  n_list * n_kv_heads * -(-(n_heads // n_kv_heads) // 16))
     lib = _load(*attention_mma_library(head_dim))
     _check(lib.sllm_attn_mma(
         _ptr(q), c_int64(q.stride(0)), _ptr(pages), _ptr(block_table),

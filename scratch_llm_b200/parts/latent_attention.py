@@ -38,6 +38,12 @@ from .linear import Linear
 from .registry import register_mixer
 
 
+#: cached vectors of up to this many entries: the split decode kernel's last CTA merges the
+#: splits itself.  Beyond it the merge kernel, which spreads a row's heads over CTAs, is faster
+#: than one CTA walking 16 heads of long vectors (at 256 entries: 13 + 8 us against 26 us).
+MERGE_INSIDE_MAX_DIM = 128
+
+
 @register_mixer("latent_attention")
 class LatentAttention(Mixer):
     pad_safe = True   # padding tokens are not stored; rows without tokens leave the kernels
@@ -190,4 +196,5 @@ class LatentAttention(Mixer):
                                       dtype=torch.float32, device=q.device)
             ops.attention_mma(*common, batch.single_rows, batch.n_single, 1, H, 1, Dp, self.scale,
                               None, split=True, n_splits=n_splits, scratch=scratch,
-                              merge_inside=base * n_splits <= ops.attention_decode_slots(Dp))
+                              merge_inside=Dp <= MERGE_INSIDE_MAX_DIM
+                              and base * n_splits <= ops.attention_decode_slots(Dp))

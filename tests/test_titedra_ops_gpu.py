@@ -267,6 +267,7 @@ LATENT = [  # heads, dim, rot_dim, vdim, q_rank, kv_rank, width, page
     (3, 8, 8, 10, 40, 20, 48, 8),          # of 28, kept as 32
     (2, 20, 10, 12, 64, 48, 72, 16),       # of 58, kept as 64; a value size below the key's
     (16, 32, 32, 32, 96, 96, 128, 16),     # of 128, many heads on one cached vector
+    (20, 16, 16, 24, 64, 48, 96, 16),      # of 64, more heads than one tile of queries holds
     (1, 8, 28, 16, 36, 36, 40, 32),        # one head, a rotated part larger than the rest
     (2, 16, 32, 40, 48, 256, 64, 64)]      # of 288: beyond the tensor-core kernels' sizes
 
