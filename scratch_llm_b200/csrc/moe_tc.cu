@@ -64,9 +64,23 @@ __device__ __forceinline__ void store_row32(float* dst, const float (&o)[32], in
 }
 
 // n_out: output features per expert (GATED: the gated size F, W holds 2 F rows per expert).
-// Tile index t: row tile t % n_row_tiles (fastest, so that an expert's row tiles, which share
-// its weights, run side by side), feature block t / n_row_tiles.
+// Tiles are walked band by band (tile_coords): a band is MOE_BAND neighbouring row tiles through
+// all feature blocks, row tiles fastest (so that an expert's row tiles, which share its weights,
+// run side by side).  A band's activations (MOE_BAND x 128 rows) stay in L2 while the weights
+// stream past once; without bands a step of many thousand rows re-reads all its activations
+// from memory for every feature block.  Up to MOE_BAND row tiles: one band.
 // SQRELU (not gated): the stored value is relu(y)^2, an expert without a gate.
+constexpr int MOE_BAND = 16;
+__device__ __forceinline__ void tile_coords(int tile, int n_row_tiles, int tiles_n, int& row_tile,
+                                            int& n_blk) {
+    const int band_tiles = MOE_BAND * tiles_n;
+    const int band = tile / band_tiles;
+    const int in_band = tile - band * band_tiles;
+    const int rows_here = min(MOE_BAND, n_row_tiles - band * MOE_BAND);
+    n_blk = in_band / rows_here;
+    row_tile = band * MOE_BAND + in_band - n_blk * rows_here;
+}
+
 template <bool GATED, typename TOut, bool SQRELU = false>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 moe_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
@@ -118,8 +132,9 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
             uint32_t it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int* t = meta + 1 + 3 * (tile % n_row_tiles);
-                const int n_blk = tile / n_row_tiles;
+                int row_tile, n_blk;
+                tile_coords(tile, n_row_tiles, tiles_n, row_tile, n_blk);
+                const int* t = meta + 1 + 3 * row_tile;
                 const int expert = t[0], m0 = t[1];
                 const int w_base = expert * rows_per_expert;
                 const int w_row0 = w_base + (GATED ? n_blk * 128 : n_blk * TN);
@@ -168,8 +183,9 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
         uint32_t local = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
             const uint32_t buf = local & 1;
-            const int* t = meta + 1 + 3 * (tile % n_row_tiles);
-            const int n_blk = tile / n_row_tiles;
+            int row_tile, n_blk;
+            tile_coords(tile, n_row_tiles, tiles_n, row_tile, n_blk);
+            const int* t = meta + 1 + 3 * row_tile;
             const int m0 = t[1], rows = t[2];
             const int r = quad * 32 + lane;
             if (!mbar_wait(&acc_full[buf], (local >> 1) & 1, 3)) break;

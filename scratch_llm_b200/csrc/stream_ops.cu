@@ -295,6 +295,32 @@ __global__ void concat_cast_kernel(const float* __restrict__ a, const float* __r
     }
 }
 
+// concat_cast_kernel for d a multiple of 8 and 16-byte aligned rows: a thread takes 8
+// neighbouring entries of one of the two streams (two 16-byte loads) and stores them at once.
+template <typename T>
+__global__ void concat_cast_vec_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                       T* __restrict__ out, int64_t total8, int d) {
+    pdl_wait();
+    pdl_trigger();
+    const int per_row = 2 * d / 8;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total8;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t n = i / per_row;
+        const int e = (int)(i - n * per_row) * 8;
+        const float* src = e < d ? a + n * d + e : b + n * d + (e - d);
+        const float4 lo = *reinterpret_cast<const float4*>(src);
+        const float4 hi = *reinterpret_cast<const float4*>(src + 4);
+        T* dst = out + n * 2 * d + e;
+        if constexpr (sizeof(T) == 4) {
+            *reinterpret_cast<float4*>(dst) = lo;
+            *reinterpret_cast<float4*>(dst + 4) = hi;
+        } else {
+            const float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+            Vec<T>::store(dst, v);
+        }
+    }
+}
+
 }  // namespace sllm
 
 using namespace sllm;
@@ -304,6 +330,16 @@ SLLM_EXPORT int sllm_concat_cast(const float* a, const float* b, void* out, int 
     if (n_rows <= 0) return 0;
     if (d <= 0) return (int)cudaErrorInvalidValue;
     const int64_t total = (int64_t)n_rows * 2 * d;
+    if (d % 8 == 0 && !(((uintptr_t)a | (uintptr_t)b | (uintptr_t)out) & 15) && dtype >= 0 &&
+        dtype <= 1) {
+        const int64_t total8 = total / 8;
+        const int vblocks = (int)((total8 + 255) / 256 > 148 * 16 ? 148 * 16 : (total8 + 255) / 256);
+        if (dtype == 0)
+            return (int)sllm_launch_pdl(concat_cast_vec_kernel<float>, dim3(vblocks), dim3(256), 0,
+                                        stream, a, b, (float*)out, total8, d);
+        return (int)sllm_launch_pdl(concat_cast_vec_kernel<__nv_bfloat16>, dim3(vblocks), dim3(256),
+                                    0, stream, a, b, (__nv_bfloat16*)out, total8, d);
+    }
     const int blocks = (int)((total + 255) / 256 > 4096 ? 4096 : (total + 255) / 256);
     if (dtype == 0)
         return (int)sllm_launch_pdl(concat_cast_kernel<float>, dim3(blocks), dim3(256), 0, stream,

@@ -186,10 +186,11 @@ def test_products_per_head_of_steps_of_few_tokens(n, H, K, J, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_stream_joins_the_embedding_output(dtype):
+@pytest.mark.parametrize("d", [40, 37])      # rows that move 16 bytes at a time, and not
+def test_stream_joins_the_embedding_output(d, dtype):
     from scratch_llm_b200.parts.stream_join import ConcatLinear
     g = torch.Generator().manual_seed(2)
-    n, d = 13, 40
+    n = 13
     x, first = torch.randn((n, d), generator=g), torch.randn((n, d), generator=g) * 4
     w = bf16_exact(torch.randn((d, 2 * d), generator=g) * (2 * d) ** -0.5)
     join = ConcatLinear(d, "")
