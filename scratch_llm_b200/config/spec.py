@@ -34,12 +34,15 @@ class LayerSpec:
     which registry each role's part comes from, is the block class's statement (its ``ROLES``):
     a layer with other roles (no feed-forward, four norms) needs another block class and
     nothing else.  ``prefix`` is the tensor-name prefix of the layer's weights; ``names`` gives
-    the sub-prefix of each role below it (default: the role's name)."""
+    the sub-prefix of each role below it (default: the role's name).  ``block_args``: constants of
+    the arrangement itself (a multiplier on what the layer adds to the stream), handed to the
+    block's constructor beside its parts."""
 
     prefix: str
     block: str
     parts: Mapping[str, PartSpec]
     names: Mapping[str, str] = field(default_factory=dict)
+    block_args: Mapping[str, Any] = field(default_factory=dict)
 
 
 def standard_layer(prefix: str, block: str, mixer: PartSpec, feed_forward: PartSpec,
@@ -99,6 +102,10 @@ class ModelSpec:
     position_sinusoid_base: float = 0.0
     #: joins of the stream with the embedding output, which runs name by index (``Run.join``)
     joins: tuple[JoinSpec, ...] = ()
+    #: a norm that the embedded tokens pass before the first layer (the stream becomes its
+    #: output, in 32-bit), with its tensor-name prefix; None: the embedding as it is
+    embed_norm: PartSpec | None = None
+    embed_norm_name: str = ""
 
     def __post_init__(self) -> None:
         if self.position_sinusoid_base < 0:

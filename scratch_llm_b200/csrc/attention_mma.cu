@@ -123,6 +123,10 @@ struct AttnArgs {
     // softmax's denominator of head h, once, with no value behind it (with several splits it is
     // added where the splits are merged).  Both in natural units, as the scores' scale.
     const float* slopes = nullptr; const float* sinks = nullptr;
+    // softcap2 > 0: the scaled score s (base-2 units) becomes softcap2 * tanh(s / softcap2), before
+    // the slopes (softcap2 is the cap times log2 e).  chunk > 0: the query at position p sees only
+    // keys from floor(p / chunk) * chunk on (positions count from the sequence's start).
+    float softcap2 = 0.f; int chunk = 0;
     // gate (may be null): [tokens, gate_stride] with head h at columns [h*HD, (h+1)*HD), as out:
     // every output element is multiplied by sigmoid(gate) before it is stored (an output gate on
     // the heads; with several splits where they are merged).
@@ -141,6 +145,17 @@ struct AttnArgs {
     // that no merge kernel follows; nobody waits for anybody.  nullptr: a merge kernel follows.
     int* merge_count;
 };
+
+// The first key position that the query at position p sees (the causal bound is the caller's).
+__device__ __forceinline__ int key_from(const AttnArgs& a, int p) {
+    int lo = a.window > 0 ? p - a.window + 1 : 0;
+    if (a.chunk > 0) lo = max(lo, p / a.chunk * a.chunk);
+    return lo;
+}
+// A scaled score (base-2 units) after the tanh cap, if the launch has one.
+__device__ __forceinline__ float capped(const AttnArgs& a, float s2) {
+    return a.softcap2 > 0.f ? a.softcap2 * tanhf(s2 / a.softcap2) : s2;
+}
 
 template <bool SPLIT>
 __global__ void __launch_bounds__(THREADS, SPLIT ? 3 : 2) attn_mma_kernel(const AttnArgs a) {
@@ -175,6 +190,7 @@ __global__ void __launch_bounds__(THREADS, SPLIT ? 3 : 2) attn_mma_kernel(const 
     const int last_pos = pos0 + min(n_packed - 1, q0 + M::BQ - 1) / GS;
     int k_lo = 0;
     if (a.window > 0) k_lo = max(0, first_pos - a.window + 1) / BKV * BKV;
+    if (a.chunk > 0) k_lo = max(k_lo, first_pos / a.chunk * a.chunk / BKV * BKV);
     const int n_tiles = (last_pos - k_lo) / BKV + 1;
     const int per_split = (n_tiles + n_splits - 1) / n_splits;
     const int tile_begin = split * per_split;
@@ -263,7 +279,7 @@ __global__ void __launch_bounds__(THREADS, SPLIT ? 3 : 2) attn_mma_kernel(const 
         if (a.slopes) slope2[h] = a.slopes[head] * LOG2E;
         if (a.sinks) sink2[h] = a.sinks[head] * LOG2E;
     }
-    const bool warp_full = a.window <= 0 && a.slopes == nullptr;
+    const bool warp_full = a.window <= 0 && a.slopes == nullptr && a.chunk <= 0 && a.softcap2 <= 0.f;
     const int warp_first_pos = pos0 + min(q0 + wq, n_packed - 1) / GS;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     float o[DTILES][4];
@@ -320,9 +336,9 @@ __global__ void __launch_bounds__(THREADS, SPLIT ? 3 : 2) attn_mma_kernel(const 
                 for (int e = 0; e < 4; ++e) {
                     const int h = e >> 1;
                     const int kpos = kt + nt * 8 + (lane & 3) * 2 + (e & 1);
-                    const bool ok = qvalid[h] && kpos <= qpos[h] &&
-                                    (a.window <= 0 || kpos > qpos[h] - a.window);
-                    s[nt][e] = ok ? s[nt][e] * a.scale_log2 - slope2[h] * (float)(qpos[h] - kpos)
+                    const bool ok = qvalid[h] && kpos <= qpos[h] && kpos >= key_from(a, qpos[h]);
+                    s[nt][e] = ok ? capped(a, s[nt][e] * a.scale_log2) -
+                                        slope2[h] * (float)(qpos[h] - kpos)
                                   : -INFINITY;
                     mx[h] = fmaxf(mx[h], s[nt][e]);
                 }
@@ -512,6 +528,7 @@ __global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnAr
     const int last_pos = pos0 + min(n_packed - 1, q0 + M::BQ - 1) / GS;
     int k_lo = 0;
     if (a.window > 0) k_lo = max(0, first_pos - a.window + 1) / BKV * BKV;
+    if (a.chunk > 0) k_lo = max(k_lo, first_pos / a.chunk * a.chunk / BKV * BKV);
     const int n_tiles = (last_pos - k_lo) / BKV + 1;
     const int per_split = (n_tiles + n_splits - 1) / n_splits;
     const int tile_begin = split * per_split;
@@ -669,7 +686,7 @@ __global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnAr
         if (a.slopes) slope2[h] = a.slopes[head] * LOG2E;
         if (a.sinks) sink2[h] = a.sinks[head] * LOG2E;
     }
-    const bool no_window = a.window <= 0 && a.slopes == nullptr;
+    const bool no_window = a.window <= 0 && a.slopes == nullptr && a.chunk <= 0 && a.softcap2 <= 0.f;
     const int first_q_pos = pos0 + min(q0, n_packed - 1) / GS;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     float o[CS_OT][4];
@@ -751,9 +768,9 @@ __global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnAr
                 for (int e = 0; e < 4; ++e) {
                     const int h = e >> 1;
                     const int kpos = kt + nt * 8 + (lane & 3) * 2 + (e & 1);
-                    const bool ok = qvalid[h] && kpos <= qpos[h] &&
-                                    (a.window <= 0 || kpos > qpos[h] - a.window);
-                    s[nt][e] = ok ? s[nt][e] * a.scale_log2 - slope2[h] * (float)(qpos[h] - kpos)
+                    const bool ok = qvalid[h] && kpos <= qpos[h] && kpos >= key_from(a, qpos[h]);
+                    s[nt][e] = ok ? capped(a, s[nt][e] * a.scale_log2) -
+                                        slope2[h] * (float)(qpos[h] - kpos)
                                   : -INFINITY;
                     mx[h] = fmaxf(mx[h], s[nt][e]);
                 }
@@ -1037,9 +1054,9 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
                               float scale, int window, int split, int n_splits, float* scratch,
                               int64_t n_tokens_total, const float* slopes, const float* sinks,
                               const void* gate, int64_t gate_stride, int* merge_count,
-                              int planes, cudaStream_t stream) {
+                              int planes, float softcap, int chunk, cudaStream_t stream) {
     if (n_list <= 0 || max_new <= 0) return 0;
-    if (planes < 1 || planes > 2) return (int)cudaErrorInvalidValue;
+    if (planes < 1 || planes > 2 || chunk < 0 || softcap < 0.f) return (int)cudaErrorInvalidValue;
     if (H <= 0 || G <= 0 || H % G != 0 || page_size <= 0 || window < 0 || n_list > 65535 ||
         G > 65535 || (q_stride % 8) != 0 || (out_stride % 2) != 0)
         return (int)cudaErrorInvalidValue;
@@ -1058,6 +1075,7 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
     a.cos_t = nullptr; a.sin_t = nullptr; a.interleaved = 1; a.write_kv = 0;
     a.planes = planes;
     a.H = H; a.G = G; a.scale_log2 = scale * 1.4426950408889634f; a.window = window;
+    a.softcap2 = softcap * 1.4426950408889634f; a.chunk = chunk;
     const int GS = H / G;
     cudaError_t e;
     if (!split) {

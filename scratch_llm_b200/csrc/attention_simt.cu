@@ -36,7 +36,8 @@ attn_simt_kernel(const T* __restrict__ q, int64_t q_stride, const T* __restrict_
                  const int* __restrict__ block_table, int table_stride, int page_size,
                  const int* __restrict__ row_start, const int* __restrict__ row_pos0,
                  T* __restrict__ out, int64_t out_stride, int H, int G, float scale, int window,
-                 const float* __restrict__ slopes, const float* __restrict__ sinks, int planes) {
+                 const float* __restrict__ slopes, const float* __restrict__ sinks, int planes,
+                 float softcap, int chunk) {
     extern __shared__ float smem[];
     __shared__ long long key_base[BKV];  // element offset of each key's K row, -1 if absent
     float* Qs = smem;
@@ -55,6 +56,7 @@ attn_simt_kernel(const T* __restrict__ q, int64_t q_stride, const T* __restrict_
     const int last_pos = first_pos + nq - 1;
     int k_lo = 0;
     if (window > 0) k_lo = max(0, first_pos - window + 1) / BKV * BKV;
+    if (chunk > 0) k_lo = max(k_lo, first_pos / chunk * chunk / BKV * BKV);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const float slope = slopes ? slopes[h] : 0.f;
@@ -113,8 +115,10 @@ attn_simt_kernel(const T* __restrict__ q, int64_t q_stride, const T* __restrict_
             for (int d = 0; d < HD; ++d) dot = fmaf(qi[d], kj[d], dot);
             const int qpos = first_pos + i;
             const bool valid = i < nq && kpos <= qpos && (window <= 0 || kpos > qpos - window) &&
-                               key_base[lane] >= 0;
-            const float s = valid ? dot * scale - slope * (float)(qpos - kpos) : -INFINITY;
+                               (chunk <= 0 || kpos >= qpos / chunk * chunk) && key_base[lane] >= 0;
+            float sc = dot * scale;
+            if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
+            const float s = valid ? sc - slope * (float)(qpos - kpos) : -INFINITY;
             const float m_new = fmaxf(m[a], warp_max(s));
             float p = 0.f, corr = 1.f;
             if (m_new != -INFINITY) {
@@ -175,15 +179,18 @@ SLLM_EXPORT int sllm_attn_simt_head_dim() { return HD; }
 // max_new: the largest number of new tokens of any row.  window: 0 = all keys.
 // slopes (may be null): float [H]; slopes[h] * (query position - key position) is taken off the
 // scaled score of head h.  sinks (may be null): float [H]; exp(sinks[h]) is added to the softmax's
-// denominator of head h, once, with no value behind it.
+// denominator of head h, once, with no value behind it.  softcap > 0: the scaled score s becomes
+// softcap * tanh(s / softcap) (before the slopes).  chunk > 0: the query at position p sees only
+// keys from floor(p / chunk) * chunk on (positions count from the sequence's start).
 SLLM_EXPORT int sllm_attn_simt(const void* q, int64_t q_stride, const void* pages,
                                const int* block_table, int table_stride, int page_size,
                                const int* row_start, const int* row_pos0, void* out,
                                int64_t out_stride, int n_rows, int max_new, int H, int G,
                                float scale, int window, const float* slopes, const float* sinks,
-                               int planes, int dtype, cudaStream_t stream) {
+                               int planes, float softcap, int chunk, int dtype,
+                               cudaStream_t stream) {
     if (n_rows <= 0 || max_new <= 0) return 0;
-    if (H <= 0 || G <= 0 || H % G != 0 || page_size <= 0 || window < 0 || planes < 1 || planes > 2)
+    if (H <= 0 || G <= 0 || H % G != 0 || page_size <= 0 || window < 0 || chunk < 0 || planes < 1 || planes > 2)
         return (int)cudaErrorInvalidValue;
     if (n_rows > 65535 || H > 65535) return (int)cudaErrorInvalidValue;
     const size_t smem = smem_floats() * sizeof(float);
@@ -196,7 +203,7 @@ SLLM_EXPORT int sllm_attn_simt(const void* q, int64_t q_stride, const void* page
         attn_simt_kernel<float><<<grid, THREADS, smem, stream>>>(
             (const float*)q, q_stride, (const float*)pages, block_table, table_stride, page_size,
             row_start, row_pos0, (float*)out, out_stride, H, G, scale, window, slopes, sinks,
-            planes);
+            planes, softcap, chunk);
     } else if (dtype == 1) {
         e = cudaFuncSetAttribute(attn_simt_kernel<__nv_bfloat16>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -204,7 +211,7 @@ SLLM_EXPORT int sllm_attn_simt(const void* q, int64_t q_stride, const void* page
         attn_simt_kernel<__nv_bfloat16><<<grid, THREADS, smem, stream>>>(
             (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, block_table,
             table_stride, page_size, row_start, row_pos0, (__nv_bfloat16*)out, out_stride, H, G,
-            scale, window, slopes, sinks, planes);
+            scale, window, slopes, sinks, planes, softcap, chunk);
     } else {
         return (int)cudaErrorInvalidValue;
     }

@@ -35,6 +35,18 @@
 // token); a row reads its state from its slot and writes it back; rows without tokens touch
 // nothing.
 //
+//
+// A decay per key CHANNEL (log_decay != null: float [tokens, H * D], the logarithm of each
+// channel's factor, at most 0): S <- diag(g) S in the rule's first line.  With L_t now the vector
+// of the channels' sums of log g up to token t of the chunk, the same unrolling holds with
+//     p_t = S0^T (e^{L_t} * k_t),   r_t = S0^T (e^{L_t} * q_t),
+//     weights  sum_d k_s[d] x_t[d] e^{L_t[d] - L_s[d]}   (x = k for s < t, x = q for s <= t),
+//     S = diag(e^{L_last}) S0 + sum_s (e^{L_last - L_s} * k_s) u_s^T.
+// Every exponent that is formed is at most 0 (a later token's sum minus an earlier one's), so
+// nothing overflows however strong the decay; the weights cost one exponential per channel and
+// pair of tokens, shared by the CTA's 16 columns.  The step size then comes from column b_col +
+// head of `ab`, and A_log / dt_bias are the caller's business (they are inside log_decay).
+//
 // Compiled once per key size: -DSLLM_HEAD_DIM=<D>.
 #include "common.cuh"
 
@@ -61,17 +73,23 @@ struct DeltaArgs {
     const int* row_start; const int* row_slot;
     float* out;                          // [tokens, H * V]
     int H; int G; int V;
+    // a decay per key channel: [tokens, >= H * D] logarithms (null: one decay per head from a)
+    const float* log_decay; int64_t ld_decay;
+    int b_col;                           // the step input of head h is ab[b_col + h]
 };
+// the kernel for a decay per channel stages a third [TC][D] table in (static) shared memory
+constexpr bool CHANNEL_FITS = D <= 192;
 
 // One token of one column by one warp: the rule as it stands.  Every warp norms the key and
 // the query itself (its lanes hold the same quads of them as of its column).  S: the lane's
 // elements of the column (already loaded), st: where they live.
-template <typename T>
+template <typename T, bool CHANNEL>
 __device__ __forceinline__ void single_token(const DeltaArgs& a, float* S, float* st, int t0,
                                              int head, int g, int col, bool live, int lane) {
     const T* act = reinterpret_cast<const T*>(a.act);
     const int64_t k_col0 = (int64_t)a.G * D, v_col0 = 2 * (int64_t)a.G * D;
-    const float decay_rate = expf(a.A_log[head]), dt_bias = a.dt_bias[head];
+    const float decay_rate = CHANNEL ? 0.f : expf(a.A_log[head]);
+    const float dt_bias = CHANNEL ? 0.f : a.dt_bias[head];
     const float q_scale = rsqrtf((float)D);
         float kq[4 * QPL], qq[4 * QPL];
         float sk = 0.f, sq = 0.f;
@@ -90,9 +108,21 @@ __device__ __forceinline__ void single_token(const DeltaArgs& a, float* S, float
         sq = warp_sum(sq);
         const float ik = 1.0f / sqrtf(sk + 1e-6f), iq = q_scale / sqrtf(sq + 1e-6f);
         const float* ab = a.ab + (int64_t)t0 * a.ld_ab;
-        const float x = ab[head] + dt_bias;
-        const float decay = expf(-decay_rate * (x > 20.f ? x : log1pf(expf(x))));
-        const float beta = 1.0f / (1.0f + expf(-ab[a.H + head]));
+        float decay = 1.f;
+        if (CHANNEL) {      // this lane's channels fade by their own factors
+            const float* lg = a.log_decay + (int64_t)t0 * a.ld_decay + (int64_t)head * D;
+#pragma unroll
+            for (int i = 0; i < QPL; ++i)
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const int e = (i * 32 + lane) * 4 + w;
+                    if (e < D) S[4 * i + w] *= expf(lg[e]);
+                }
+        } else {
+            const float x = ab[head] + dt_bias;
+            decay = expf(-decay_rate * (x > 20.f ? x : log1pf(expf(x))));
+        }
+        const float beta = 1.0f / (1.0f + expf(-ab[a.b_col + head]));
         const float value = live ? to_float(act[(int64_t)t0 * a.ld_act + v_col0 +
                                                 (int64_t)head * a.V + col]) : 0.f;
         float p = 0.f, rq = 0.f, kdq = 0.f;
@@ -100,7 +130,7 @@ __device__ __forceinline__ void single_token(const DeltaArgs& a, float* S, float
         for (int i = 0; i < 4 * QPL; ++i) {
             kq[i] *= ik;
             qq[i] *= iq;
-            S[i] *= decay;
+            if (!CHANNEL) S[i] *= decay;
             p = fmaf(S[i], kq[i], p);
             rq = fmaf(S[i], qq[i], rq);
             kdq = fmaf(kq[i], qq[i], kdq);
@@ -125,7 +155,7 @@ __device__ __forceinline__ void single_token(const DeltaArgs& a, float* S, float
 // Steps in which every row brings one token (decoding): 4 warps = 4 columns per CTA, few
 // registers, so that many CTAs share an SM and the states stream at the memory's rate.
 constexpr int STEP_COLS = 4;
-template <typename T>
+template <typename T, bool CHANNEL>
 __global__ void __launch_bounds__(32 * STEP_COLS) delta_rule_step_kernel(const DeltaArgs a) {
     pdl_wait();
     pdl_trigger();
@@ -148,12 +178,12 @@ __global__ void __launch_bounds__(32 * STEP_COLS) delta_rule_step_kernel(const D
             for (int w = 0; w < 4; ++w) S[4 * i + w] = (live && e + w < D) ? st[e + w] : 0.f;
         }
     }
-    single_token<T>(a, S, st, t0, head, head / (a.H / a.G), col, live, lane);
+    single_token<T, CHANNEL>(a, S, st, t0, head, head / (a.H / a.G), col, live, lane);
 }
 
 // VECTOR: keys and queries are fetched in 16-byte pieces (D a multiple of 16 / sizeof(T), rows
 // and base 16-byte aligned); else element by element.
-template <typename T, bool VECTOR>
+template <typename T, bool VECTOR, bool CHANNEL>
 __global__ void __launch_bounds__(THREADS) delta_rule_kernel(const DeltaArgs a) {
     constexpr int VEC = VECTOR ? 16 / (int)sizeof(T) : 1;
     constexpr int PER_ROW = D / VEC;                               // pieces of a key or query
@@ -169,6 +199,10 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(const DeltaArgs a) 
     // s <= t; zero elsewhere
     __shared__ float weight[2 * TC][TC + 1];
     __shared__ float log_g[TC], cum_s[TC], beta_s[TC], grow_s[TC], rest_s[TC];
+    // a decay per channel: the channels' log decays of the chunk's tokens, then their running
+    // sums L_t, and at last e^{L_t} * k_t (the keys that meet S0); last_s: L of the chunk's last token
+    __shared__ __align__(16) float lam[CHANNEL ? TC : 1][CHANNEL ? LDK : 4];
+    __shared__ float last_s[CHANNEL ? LDK : 4];
 
     pdl_wait();
     pdl_trigger();
@@ -192,18 +226,21 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(const DeltaArgs a) 
             const int e = (i * 32 + lane) * 4 + w;
             S[4 * i + w] = (live && e < D) ? st[e] : 0.f;
         }
-    const float decay_rate = expf(a.A_log[head]), dt_bias = a.dt_bias[head];
+    const float decay_rate = CHANNEL ? 0.f : expf(a.A_log[head]);
+    const float dt_bias = CHANNEL ? 0.f : a.dt_bias[head];
     const float q_scale = rsqrtf((float)D);
 
     if (n_new == 1) {   // decoding: no shared memory, no barrier
-        single_token<T>(a, S, st, t0, head, g, col, live, lane);
+        single_token<T, CHANNEL>(a, S, st, t0, head, g, col, live, lane);
         return;
     }
     // columns beyond D (where D is no multiple of 4) stay zero for good
     for (int idx = tid; idx < TC * LDK; idx += THREADS) {
         (&ks[0][0])[idx] = 0.f;
         (&qs[0][0])[idx] = 0.f;
+        if (CHANNEL) (&lam[0][0])[idx] = 0.f;
     }
+    if (CHANNEL && tid < LDK) last_s[tid] = 0.f;
     Piece raw[QK_ITEMS];
     T raw_v = from_float<T>(0.f);
     float raw_a = 0.f, raw_b = 0.f;
@@ -229,8 +266,8 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(const DeltaArgs a) 
         }
         if (tid < nt) {
             const float* ab = a.ab + (int64_t)(t0 + c0 + tid) * a.ld_ab;
-            raw_a = ab[head];
-            raw_b = ab[a.H + head];
+            raw_a = CHANNEL ? 0.f : ab[head];
+            raw_b = ab[a.b_col + head];
         }
     };
     auto commit = [&](int nt) {    // what fetch() requested, into shared memory as 32-bit
@@ -268,6 +305,13 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(const DeltaArgs a) 
         const int nt = min(TC, n_new - c0);
         __syncthreads();   // the previous chunk's staging is no longer read
         commit(nt);
+        if (CHANNEL) {     // the chunk's log decays per channel (zeros beyond its tokens)
+            const float* lg = a.log_decay + (int64_t)(t0 + c0) * a.ld_decay + (int64_t)head * D;
+            for (int idx = tid; idx < TC * D; idx += THREADS) {
+                const int t = idx / D, e = idx - t * D;
+                lam[t][e] = t < nt ? lg[(int64_t)t * a.ld_decay + e] : 0.f;
+            }
+        }
         if (c0 + TC < n_new) fetch(c0 + TC);   // in flight while this chunk is worked on
         __syncthreads();
         // unit vectors and the query's scale: one warp per token
@@ -286,7 +330,18 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(const DeltaArgs a) 
                 qs[t][e] *= iq;
             }
         }
-        if (tid >= THREADS - TC) {   // (the last warp: it has no token to norm unless nt is 16)
+        if (CHANNEL) {               // running sums of the log decays, channel by channel
+            // (warps nt .. 15 have no token to norm; with a full chunk everyone shares the work)
+            for (int e = tid; e < D; e += THREADS) {
+                float c = 0.f;
+#pragma unroll
+                for (int t = 0; t < TC; ++t) {
+                    c += lam[t][e];
+                    lam[t][e] = c;
+                }
+                last_s[e] = lam[nt - 1][e];
+            }
+        } else if (tid >= THREADS - TC) {   // (the last warp: it has no token to norm unless nt is 16)
             const int t = tid - (THREADS - TC);
             float c = 0.f, last = 0.f;
             for (int i = 0; i < TC; ++i) {
@@ -305,7 +360,11 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(const DeltaArgs a) 
             const bool with_q = row >= TC;
             float dot = 0.f;
             const bool used = t < nt && s < nt && (with_q ? s <= t : s < t);
-            if (used) {
+            if (used && CHANNEL) {
+                const float* x = with_q ? &qs[t][0] : &ks[t][0];
+                for (int e = 0; e < D; ++e)
+                    dot = fmaf(x[e] * ks[s][e], expf(lam[t][e] - lam[s][e]), dot);
+            } else if (used) {
                 const float* x = with_q ? &qs[t][0] : &ks[t][0];
 #pragma unroll 4
                 for (int c = 0; c < QUADS; ++c) {
@@ -318,6 +377,18 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(const DeltaArgs a) 
             weight[row][s] = with_q ? dot : -dot;
         }
         __syncthreads();
+        if (CHANNEL) {
+            // what the rest of the chunk needs: e^{L_t} * k_t (in lam's place) and e^{L_t} * q_t for
+            // the products with S0, and e^{L_last - L_t} * k_t for the state's update
+            for (int idx = tid; idx < TC * D; idx += THREADS) {
+                const int t = idx / D, e = idx - t * D;
+                const float L = lam[t][e], grow = expf(L), k = ks[t][e];
+                lam[t][e] = grow * k;
+                qs[t][e] *= grow;
+                ks[t][e] = t < nt ? k * expf(last_s[e] - L) : 0.f;
+            }
+            __syncthreads();
+        }
 
         // ---- this lane's share of S0^T k_t (v[t]) and S0^T q_t (v[16 + t])
         float v[2 * TC];
@@ -328,7 +399,8 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(const DeltaArgs a) 
             for (int i = 0; i < QPL; ++i) {
                 const int c = i * 32 + lane;
                 if (c < QUADS) {
-                    const float4 kt = *reinterpret_cast<const float4*>(&ks[t][4 * c]);
+                    const float4 kt = *reinterpret_cast<const float4*>(
+                        CHANNEL ? &lam[t][4 * c] : &ks[t][4 * c]);
                     const float4 qt = *reinterpret_cast<const float4*>(&qs[t][4 * c]);
                     pk += S[4 * i] * kt.x + S[4 * i + 1] * kt.y + S[4 * i + 2] * kt.z +
                           S[4 * i + 3] * kt.w;
@@ -354,7 +426,8 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(const DeltaArgs a) 
         }
         // lane t < 16: the sum that becomes u_t; lane 16 + t: the sum that becomes o_t
         const int t_mine = lane & 15;
-        float acc = lane < TC ? vs[t_mine][warp] - grow_s[t_mine] * v[0] : grow_s[t_mine] * v[0];
+        const float grow_mine = CHANNEL ? 1.f : grow_s[t_mine];   // (per channel: inside v[0])
+        float acc = lane < TC ? vs[t_mine][warp] - grow_mine * v[0] : grow_mine * v[0];
         const float beta_mine = lane < TC ? beta_s[t_mine] : 0.f;
         float u[TC];
 #pragma unroll
@@ -365,12 +438,23 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(const DeltaArgs a) 
         if (lane >= TC && t_mine < nt && live)
             a.out[(int64_t)(t0 + c0 + t_mine) * a.H * a.V + (int64_t)head * a.V + col] = acc;
         // ---- the state after the chunk
-        const float keep_all = grow_s[nt - 1];
+        if (CHANNEL) {
 #pragma unroll
-        for (int i = 0; i < 4 * QPL; ++i) S[i] *= keep_all;
+            for (int i = 0; i < QPL; ++i)
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const int e = (i * 32 + lane) * 4 + w;
+                    if (e < D) S[4 * i + w] *= expf(last_s[e]);
+                }
+        } else {
+            const float keep_all = grow_s[nt - 1];
+#pragma unroll
+            for (int i = 0; i < 4 * QPL; ++i) S[i] *= keep_all;
+        }
 #pragma unroll
         for (int t = 0; t < TC; ++t) {
-            const float f = rest_s[t] * u[t];      // (u is zero beyond the chunk's tokens)
+            // (u is zero beyond the chunk's tokens; per channel the keys carry their factors)
+            const float f = CHANNEL ? u[t] : rest_s[t] * u[t];
 #pragma unroll
             for (int i = 0; i < QPL; ++i) {
                 const int c = i * 32 + lane;
@@ -407,21 +491,29 @@ SLLM_EXPORT int sllm_delta_rule_head_dim() { return D; }
 SLLM_EXPORT int sllm_delta_rule(const void* act, int64_t ld_act, const float* ab, int64_t ld_ab,
                                 const float* A_log, const float* dt_bias, float* state,
                                 const int* row_start, const int* row_slot, float* out, int n_rows,
-                                int max_new, int H, int G, int V, int dtype, cudaStream_t stream) {
+                                int max_new, int H, int G, int V, const float* log_decay,
+                                int64_t ld_decay, int b_col, int dtype, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G != 0 || V <= 0 || n_rows > 65535 || H > 65535 ||
-        ld_act < 2 * (int64_t)G * D + (int64_t)H * V || ld_ab < 2 * H)
+        ld_act < 2 * (int64_t)G * D + (int64_t)H * V || b_col < 0 || ld_ab < b_col + H ||
+        (!log_decay && (ld_ab < H || !A_log || !dt_bias)) ||
+        (log_decay && (ld_decay < (int64_t)H * D || !CHANNEL_FITS)))
         return (int)cudaErrorInvalidValue;
     DeltaArgs a;
+    a.log_decay = log_decay; a.ld_decay = ld_decay; a.b_col = b_col;
     a.act = act; a.ld_act = ld_act; a.ab = ab; a.ld_ab = ld_ab; a.A_log = A_log;
     a.dt_bias = dt_bias; a.state = state; a.row_start = row_start; a.row_slot = row_slot;
     a.out = out; a.H = H; a.G = G; a.V = V;
     if (max_new == 1) {   // no row brings more than one token
         dim3 sgrid((V + STEP_COLS - 1) / STEP_COLS, H, n_rows);
-        if (dtype == 0) delta_rule_step_kernel<float><<<sgrid, 32 * STEP_COLS, 0, stream>>>(a);
-        else if (dtype == 1)
-            delta_rule_step_kernel<__nv_bfloat16><<<sgrid, 32 * STEP_COLS, 0, stream>>>(a);
-        else return (int)cudaErrorInvalidValue;
+        if (dtype != 0 && dtype != 1) return (int)cudaErrorInvalidValue;
+        if (log_decay) {
+            if (dtype == 0) delta_rule_step_kernel<float, true><<<sgrid, 32 * STEP_COLS, 0, stream>>>(a);
+            else delta_rule_step_kernel<__nv_bfloat16, true><<<sgrid, 32 * STEP_COLS, 0, stream>>>(a);
+        } else {
+            if (dtype == 0) delta_rule_step_kernel<float, false><<<sgrid, 32 * STEP_COLS, 0, stream>>>(a);
+            else delta_rule_step_kernel<__nv_bfloat16, false><<<sgrid, 32 * STEP_COLS, 0, stream>>>(a);
+        }
         SLLM_LAUNCH_CHECK();
         return 0;
     }
@@ -431,14 +523,23 @@ SLLM_EXPORT int sllm_delta_rule(const void* act, int64_t ld_act, const float* ab
     // 16-byte pieces need every key, query and row of `act` to start on a 16-byte boundary
     const bool vector = D % vec == 0 && ld_act % vec == 0 && ((uintptr_t)act & 15) == 0 &&
                         ((int64_t)G * D) % vec == 0;
-    if (dtype == 0) {
-        if (vector) delta_rule_kernel<float, (D % 4 == 0)><<<grid, THREADS, 0, stream>>>(a);
-        else delta_rule_kernel<float, false><<<grid, THREADS, 0, stream>>>(a);
-    } else if (dtype == 1) {
-        if (vector) delta_rule_kernel<__nv_bfloat16, (D % 8 == 0)><<<grid, THREADS, 0, stream>>>(a);
-        else delta_rule_kernel<__nv_bfloat16, false><<<grid, THREADS, 0, stream>>>(a);
+    if (dtype != 0 && dtype != 1) return (int)cudaErrorInvalidValue;
+    if (log_decay) {
+        if constexpr (CHANNEL_FITS) {
+            if (dtype == 0) {
+                if (vector) delta_rule_kernel<float, (D % 4 == 0), true><<<grid, THREADS, 0, stream>>>(a);
+                else delta_rule_kernel<float, false, true><<<grid, THREADS, 0, stream>>>(a);
+            } else {
+                if (vector) delta_rule_kernel<__nv_bfloat16, (D % 8 == 0), true><<<grid, THREADS, 0, stream>>>(a);
+                else delta_rule_kernel<__nv_bfloat16, false, true><<<grid, THREADS, 0, stream>>>(a);
+            }
+        }
+    } else if (dtype == 0) {
+        if (vector) delta_rule_kernel<float, (D % 4 == 0), false><<<grid, THREADS, 0, stream>>>(a);
+        else delta_rule_kernel<float, false, false><<<grid, THREADS, 0, stream>>>(a);
     } else {
-        return (int)cudaErrorInvalidValue;
+        if (vector) delta_rule_kernel<__nv_bfloat16, (D % 8 == 0), false><<<grid, THREADS, 0, stream>>>(a);
+        else delta_rule_kernel<__nv_bfloat16, false, false><<<grid, THREADS, 0, stream>>>(a);
     }
     SLLM_LAUNCH_CHECK();
     return 0;

@@ -204,6 +204,63 @@ lowrank_decay_kernel(const float* __restrict__ pre, int64_t ldp, const float* __
     }
 }
 
+// The second product of a low-rank pair, in 32-bit, with what follows it.  pre: float32 [N, ldp]
+// holds the hidden values (the first product's output) in columns [col0, col0 + R); w2t: float32
+// [R, C] (the second matrix, transposed); bias (may be null): float32 [C].
+//     z[n, c] = bias[c] + sum_r w2t[r, c] * pre[n, col0 + r]
+//     mode 0:  out = z
+//     mode 1:  out = -exp(rate_log[c / per_rate]) * softplus(z)    (the logarithm of a decay
+//              exp(-exp(A) softplus(z)) with one A per `per_rate` channels)
+// The sum runs over r in ascending order for every token, whatever the batch.  out: [N, C] of
+// TO.  grid (ceil(C / 256), ceil(N / LOWRANK_TOKENS)); shared: LOWRANK_TOKENS * R floats.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+lowrank_expand_kernel(const float* __restrict__ pre, int64_t ldp, int col0,
+                      const float* __restrict__ w2t, const float* __restrict__ bias,
+                      const float* __restrict__ rate_log, int per_rate, int mode,
+                      TO* __restrict__ out, int N, int C, int R) {
+    pdl_wait();
+    pdl_trigger();
+    extern __shared__ float th[];   // [LOWRANK_TOKENS][R]
+    const int n0 = blockIdx.y * LOWRANK_TOKENS;
+    const int nt = min(LOWRANK_TOKENS, N - n0);
+    for (int i = threadIdx.x; i < LOWRANK_TOKENS * R; i += blockDim.x) {
+        const int t = i / R, r = i - t * R;
+        th[t * R + r] = t < nt ? pre[(int64_t)(n0 + t) * ldp + col0 + r] : 0.f;
+    }
+    __syncthreads();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    float acc[LOWRANK_TOKENS];
+#pragma unroll
+    for (int t = 0; t < LOWRANK_TOKENS; ++t) acc[t] = 0.f;
+    int r = 0;
+    for (; r + 16 <= R; r += 16) {
+        float w[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) w[j] = w2t[(int64_t)(r + j) * C + c];
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+#pragma unroll
+            for (int t = 0; t < LOWRANK_TOKENS; ++t) acc[t] = fmaf(w[j], th[t * R + r + j], acc[t]);
+    }
+    for (; r < R; ++r) {
+        const float w = w2t[(int64_t)r * C + c];
+#pragma unroll
+        for (int t = 0; t < LOWRANK_TOKENS; ++t) acc[t] = fmaf(w, th[t * R + r], acc[t]);
+    }
+    const float b0 = bias ? bias[c] : 0.f;
+    const float rate = mode == 1 ? expf(rate_log[c / per_rate]) : 0.f;
+#pragma unroll
+    for (int t = 0; t < LOWRANK_TOKENS; ++t) {
+        if (t < nt) {
+            float z = acc[t] + b0;
+            if (mode == 1) z = -rate * (z > 20.f ? z : log1pf(expf(z)));
+            out[(int64_t)(n0 + t) * C + c] = from_float<TO>(z);
+        }
+    }
+}
+
 }  // namespace sllm
 
 using namespace sllm;
@@ -291,6 +348,30 @@ SLLM_EXPORT int sllm_lowrank_decay(const float* pre, int64_t ldp, const float* w
     if (grid.y > 65535) return (int)cudaErrorInvalidValue;
     lowrank_decay_kernel<<<grid, 256, LOWRANK_TOKENS * R * sizeof(float), stream>>>(
         pre, ldp, w2t, w0, a_bias, decay_scale, out, n_tokens, C, R);
+    SLLM_LAUNCH_CHECK();
+    return 0;
+}
+
+// out_dtype: 0 = float32, 1 = bfloat16.  mode 1 needs rate_log (float [C / per_rate]).
+SLLM_EXPORT int sllm_lowrank_expand(const float* pre, int64_t ldp, int col0, const float* w2t,
+                                    const float* bias, const float* rate_log, int per_rate,
+                                    int mode, void* out, int out_dtype, int n_tokens, int C, int R,
+                                    cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (C <= 0 || R <= 0 || R > 1024 || col0 < 0 || ldp < col0 + R || mode < 0 || mode > 1 ||
+        (mode == 1 && (!rate_log || per_rate <= 0 || C % per_rate)))
+        return (int)cudaErrorInvalidValue;
+    dim3 grid((C + 255) / 256, (n_tokens + LOWRANK_TOKENS - 1) / LOWRANK_TOKENS);
+    if (grid.y > 65535) return (int)cudaErrorInvalidValue;
+    const size_t smem = LOWRANK_TOKENS * R * sizeof(float);
+    if (out_dtype == 0)
+        lowrank_expand_kernel<float><<<grid, 256, smem, stream>>>(
+            pre, ldp, col0, w2t, bias, rate_log, per_rate, mode, (float*)out, n_tokens, C, R);
+    else if (out_dtype == 1)
+        lowrank_expand_kernel<__nv_bfloat16><<<grid, 256, smem, stream>>>(
+            pre, ldp, col0, w2t, bias, rate_log, per_rate, mode, (__nv_bfloat16*)out, n_tokens, C, R);
+    else
+        return (int)cudaErrorInvalidValue;
     SLLM_LAUNCH_CHECK();
     return 0;
 }

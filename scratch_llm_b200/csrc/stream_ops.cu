@@ -182,6 +182,25 @@ __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, 
     }
 }
 
+// A gated feed-forward's activation with clamps: with g = min(gu[n, f], limit) and
+// u = clamp(gu[n, F + f], -limit, limit),  out[n, f] = g * sigmoid(slope * g) * (u + 1), in
+// 32-bit.  out rows are ldo apart (a column slice of a wider buffer).
+template <typename T>
+__global__ void clamped_gate_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t ldo,
+                                    int64_t n_rows, int F, float limit, float slope) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t total = n_rows * F;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t n = i / F;
+        const int f = (int)(i - n * F);
+        const float g = fminf(to_float(gu[n * 2 * F + f]), limit);
+        const float u = fminf(fmaxf(to_float(gu[n * 2 * F + F + f]), -limit), limit);
+        out[n * ldo + f] = from_float<T>(g / (1.0f + expf(-slope * g)) * (u + 1.0f));
+    }
+}
+
 // x[n, c] *= sigmoid(gate[n, c]) for c < C; x rows ldx apart, gate rows ldg apart.
 template <typename T>
 __global__ void sigmoid_gate_kernel(T* __restrict__ x, int64_t ldx, const T* __restrict__ gate,
@@ -431,6 +450,19 @@ SLLM_EXPORT int sllm_gated_act(const void* gu, void* out, int n_rows, int F, int
                                                              F, act)),
         (gated_act_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
             (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_rows, F, act)));
+    return 0;
+}
+
+SLLM_EXPORT int sllm_clamped_gate(const void* gu, void* out, int64_t ldo, int n_rows, int F,
+                                  float limit, float slope, int dtype, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (F <= 0 || ldo < F || !(limit > 0.f)) return (int)cudaErrorInvalidValue;
+    const int blocks = flat_blocks((int64_t)n_rows * F, 256);
+    SLLM_BY_DTYPE(dtype,
+        (clamped_gate_kernel<float><<<blocks, 256, 0, stream>>>(
+            (const float*)gu, (float*)out, ldo, n_rows, F, limit, slope)),
+        (clamped_gate_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
+            (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, ldo, n_rows, F, limit, slope)));
     return 0;
 }
 

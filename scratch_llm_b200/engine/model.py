@@ -92,7 +92,7 @@ class DecoderModel:
                     built[role] = make(table, what, part_spec)
                     self._named_parts.append(
                         (f"{layer.prefix}.{layer.names.get(role, role)}", built[role]))
-            block = block_cls(**built)
+            block = block_cls(**built, **dict(getattr(layer, "block_args", None) or {}))
             block.parts = built          # role -> part, for whoever walks the model's parts
             block.cache_owner = next((built[r] for r, k in roles.items() if k == "mixer"), None)
             self.blocks.append(block)
@@ -117,12 +117,21 @@ class DecoderModel:
             self._next_entry.append(entry if getattr(block, "takes_next_entry", False) else None)
         self.final_norm = make(NORMS, "norm", spec.final_norm)
         self._named_parts.append((spec.final_norm_name, self.final_norm))
+        # a norm between the embedding and the first layer, for designs that have one
+        self.embed_norm = None
+        if spec.embed_norm is not None:
+            self.embed_norm = make(NORMS, "norm", spec.embed_norm)
+            if not hasattr(self.embed_norm, "in_place"):
+                raise ValueError(f"norm {spec.embed_norm.kind!r} cannot norm the stream in place, "
+                                 "which the norm after the embedding does")
+            self._named_parts.append((spec.embed_norm_name, self.embed_norm))
         # what the first run starts with, for the embedding (if that block says, its norm's
         # factor is one number per token and its gain a vector `weight`)
         first = self.blocks[spec.order[0].layer] if spec.order else None
         entry = first.entry() if first is not None and hasattr(first, "entry") else None
         self._first_entry = entry if (entry is not None and getattr(entry[0], "deferrable", False)
-                                      and hasattr(entry[1], "accepts_normed")) else None
+                                      and hasattr(entry[1], "accepts_normed")
+                                      and spec.embed_norm is None) else None
         # the last run may prepare the final norm for the output matrix in steps that want the
         # logits of every token in order (decode steps), where no rows are gathered in between
         last = self.blocks[spec.order[-1].layer] if spec.order else None
@@ -144,6 +153,8 @@ class DecoderModel:
         for part in self.joins:
             seen.setdefault(id(part), part)
         seen.setdefault(id(self.final_norm), self.final_norm)
+        if self.embed_norm is not None:
+            seen.setdefault(id(self.embed_norm), self.embed_norm)
         return list(seen.values())
 
     # --------------------------------------------------------------------------- weights
@@ -220,6 +231,20 @@ class DecoderModel:
                 st[run.cache] = a + b
                 self._state_split[run.cache] = (len(a), isinstance(mine, (tuple, list)),
                                                 len(b), isinstance(own, (tuple, list)))
+        # a run that only READS an entry may look further back than the run that writes it (a
+        # wider window, or no window at all): the entry then keeps what its farthest reader needs
+        for run in self.spec.order:
+            mixer = self.blocks[run.layer].cache_owner
+            need = mixer.kv_spec() if (not run.write and mixer is not None) else None
+            have = kv[run.cache]
+            if need is None or have is None:
+                continue
+            if (need.n_kv_heads, need.head_dim, need.planes) != \
+                    (have.n_kv_heads, have.head_dim, have.planes):
+                raise ValueError(f"layer {run.layer} reads cache entry {run.cache}, whose keys "
+                                 f"have another shape ({have} against {need})")
+            if have.window is not None and (need.window is None or need.window > have.window):
+                kv[run.cache] = KVSpec(have.n_kv_heads, have.head_dim, need.window, have.planes)
         return kv, st
 
     def _states_of(self, cache, entry: int):
@@ -287,6 +312,11 @@ class DecoderModel:
         resid = torch.empty((batch.n_tokens, s.hidden_size), dtype=torch.float32,
                             device=self.ctx.device)
         pending = self._embed(batch, resid)
+        if self.embed_norm is not None:
+            if pending is not None:
+                raise ValueError("a norm after the embedding needs an embedding that leaves "
+                                 "nothing pending")
+            self.embed_norm.in_place(resid)
         first = None
         if self._keeps_first:
             if pending is not None:

@@ -45,6 +45,8 @@ EXTRA_LIBRARIES: dict[str, tuple[tuple[str, ...], tuple[str, ...]]] = {
     "sllm_moe": (("moe.cu",), ()),
     "sllm_moe_tc": (("moe_tc.cu",), ()),
     "sllm_latent_attention": (("latent_attention.cu",), ()),
+    "sllm_layer_norm": (("layer_norm.cu",), ()),
+    "sllm_norm_rope_cache": (("norm_rope_cache.cu",), ()),
 }
 
 
@@ -578,8 +580,11 @@ def attention_simt(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tens
                    out: torch.Tensor, n_rows: int, max_new: int, n_heads: int, n_kv_heads: int,
                    head_dim: int, scale: float, window: int | None,
                    slopes: torch.Tensor | None = None,
-                   sinks: torch.Tensor | None = None) -> torch.Tensor:
+                   sinks: torch.Tensor | None = None, softcap: float = 0.0,
+                   chunk: int | None = None) -> torch.Tensor:
     """Causal attention of the packed batch over the paged cache (CUDA cores, 32-bit math).
+    ``softcap`` > 0: the scaled score s becomes ``softcap * tanh(s / softcap)``; ``chunk``: the
+    query at position p sees only keys from ``p // chunk * chunk`` on.
     ``q`` may be a column slice of a wider buffer (the fused qkv).  ``slopes`` (float32 [H]):
     ``slopes[h] * (query position - key position)`` is taken off head h's scaled scores;
     ``sinks`` (float32 [H]): ``exp(sinks[h])`` joins head h's softmax denominator once, with no
@@ -604,7 +609,8 @@ def attention_simt(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tens
         c_int(block_table.stride(0)), c_int(page_size), _ptr(row_start), _ptr(row_pos0),
         _ptr(out), c_int64(out.stride(0)), c_int(n_rows), c_int(max_new), c_int(n_heads),
         c_int(n_kv_heads), c_float(scale), c_int(window or 0), _ptr(slopes), _ptr(sinks),
-        c_int(planes), c_int(_code(q.dtype)), _stream()), "attention_simt")
+        c_int(planes), c_float(softcap), c_int(chunk or 0), c_int(_code(q.dtype)), _stream()),
+        "attention_simt")
     return out
 
 
@@ -615,9 +621,10 @@ def attention_mma(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tenso
                   window: int | None, split: bool, n_splits: int = 1,
                   scratch: torch.Tensor | None = None, slopes: torch.Tensor | None = None,
                   sinks: torch.Tensor | None = None, gate: torch.Tensor | None = None,
-                  merge_inside: bool = False) -> torch.Tensor:
+                  merge_inside: bool = False, softcap: float = 0.0,
+                  chunk: int | None = None) -> torch.Tensor:
     """Causal attention of the listed rows over the paged cache on the tensor cores
-    (bfloat16).  ``split`` False: the wide kernel for rows with many new tokens; True: the
+    (bfloat16).  ``softcap`` / ``chunk`` as in :func:`attention_simt`.  ``split`` False: the wide kernel for rows with many new tokens; True: the
     split kernel for decode rows, ``n_splits`` CTAs along the keys, partial results in
     ``scratch`` (32-bit, :func:`attention_mma_scratch_floats` entries) when ``n_splits`` > 1.
     ``slopes`` / ``sinks`` as in :func:`attention_simt`.  ``gate`` [N, H * hd] (may be a column
@@ -665,7 +672,8 @@ def attention_mma(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tenso
         c_int(n_heads), c_int(n_kv_heads), c_float(scale), c_int(window or 0),
         c_int(int(split)), c_int(n_splits), _ptr(scratch), c_int64(n_tokens), _ptr(slopes),
         _ptr(sinks), _ptr(gate), c_int64(gate.stride(0) if gate is not None else 0),
-        _ptr(counters), c_int(planes), _stream()), "attention_mma")
+        _ptr(counters), c_int(planes), c_float(softcap), c_int(chunk or 0), _stream()),
+        "attention_mma")
     return out
 
 
@@ -1005,6 +1013,21 @@ def gated_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> torc
     _check(_core("sllm_stream_ops").sllm_gated_act(
         _ptr(gate_up), _ptr(out), c_int(n), c_int(two_f // 2), c_int(ACTIVATIONS[activation]),
         c_int(_code(out.dtype)), _stream()), "gated_act")
+    return out
+
+
+def clamped_gate(gate_up: torch.Tensor, out: torch.Tensor, limit: float,
+                 slope: float) -> torch.Tensor:
+    """With g = min(gate_up[n, f], limit) and u = clamp(gate_up[n, F + f], -limit, limit):
+    out[n, f] = g * sigmoid(slope * g) * (u + 1).  ``out`` may be a column slice."""
+    _need(gate_up, None, "gate_up")
+    _need(out, gate_up.dtype, "out", contiguous=False)
+    n, two_f = gate_up.shape
+    if two_f % 2 or out.shape != (n, two_f // 2) or out.stride(1) != 1:
+        raise KernelError("clamped_gate shapes")
+    _check(_core("sllm_stream_ops").sllm_clamped_gate(
+        _ptr(gate_up), _ptr(out), c_int64(out.stride(0)), c_int(n), c_int(two_f // 2),
+        c_float(limit), c_float(slope), c_int(_code(out.dtype)), _stream()), "clamped_gate")
     return out
 
 
@@ -1493,14 +1516,23 @@ def moe_combine(y: torch.Tensor, x: torch.Tensor, shared: torch.Tensor | None, i
 def delta_rule(act: torch.Tensor, ab: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
                state: torch.Tensor, row_start: torch.Tensor, row_slot: torch.Tensor,
                out: torch.Tensor, n_rows: int, n_heads: int, n_kv_heads: int, key_dim: int,
-               value_dim: int, max_new: int = 0) -> torch.Tensor:
+               value_dim: int, max_new: int = 0, log_decay: torch.Tensor | None = None,
+               b_col: int | None = None) -> torch.Tensor:
     """The gated delta rule over the packed batch (csrc/delta_rule.cu): ``act`` [N, 2 G D + H V]
     holds query heads, key heads and value heads after the convolution; ``ab`` float32
     [N, 2 H] the decay and step inputs; ``state`` float32 [slots, H, V, D] is read and written
     at the rows' slots; ``out`` float32 [N, H * V].  ``max_new``: the most tokens a row brings,
-    if known (1 selects the kernel for decode steps; 0: not known)."""
+    if known (1 selects the kernel for decode steps; 0: not known).
+
+    ``log_decay`` (float32 [N, H * D], at most 0): a decay per key CHANNEL, given as its
+    logarithm; ``a_log`` and ``dt_bias`` are then not read (may be None), and head h's step input
+    is column ``b_col + h`` of ``ab`` (any width)."""
     _need(act, None, "act", contiguous=False)
     _need(ab, torch.float32, "ab", contiguous=False)
+    if log_decay is not None:
+        return _delta_rule_channels(act, ab, state, row_start, row_slot, out, n_rows, n_heads,
+                                    n_kv_heads, key_dim, value_dim, max_new, log_decay,
+                                    n_heads if b_col is None else b_col)
     _need(a_log, torch.float32, "A_log")
     _need(dt_bias, torch.float32, "dt_bias")
     _need(state, torch.float32, "state")
@@ -1519,8 +1551,72 @@ def delta_rule(act: torch.Tensor, ab: torch.Tensor, a_log: torch.Tensor, dt_bias
     _check(_load(*delta_rule_library(key_dim)).sllm_delta_rule(
         _ptr(act), c_int64(act.stride(0)), _ptr(ab), c_int64(ab.stride(0)), _ptr(a_log),
         _ptr(dt_bias), _ptr(state), _ptr(row_start), _ptr(row_slot), _ptr(out), c_int(n_rows),
-        c_int(max_new), c_int(n_heads), c_int(n_kv_heads), c_int(value_dim), c_int(_code(act.dtype)), _stream()),
+        c_int(max_new), c_int(n_heads), c_int(n_kv_heads), c_int(value_dim), c_void_p(0),
+        c_int64(0), c_int(n_heads), c_int(_code(act.dtype)), _stream()),
         "delta_rule")
+    return out
+
+
+#: with a decay per channel the delta-rule kernel stages a third table: key sizes up to this
+DELTA_CHANNEL_MAX_KEY_DIM = 192
+
+
+def _delta_rule_channels(act, ab, state, row_start, row_slot, out, n_rows, n_heads, n_kv_heads,
+                         key_dim, value_dim, max_new, log_decay, b_col) -> torch.Tensor:
+    _need(log_decay, torch.float32, "log_decay", contiguous=False)
+    _need(state, torch.float32, "state")
+    _need(row_start, torch.int32, "row_start")
+    _need(row_slot, torch.int32, "row_slot")
+    _need(out, torch.float32, "out")
+    n = act.shape[0]
+    if act.stride(1) != 1 or ab.stride(1) != 1 or ab.shape[0] != n \
+            or not 0 <= b_col <= ab.shape[1] - n_heads \
+            or act.shape[1] < 2 * n_kv_heads * key_dim + n_heads * value_dim \
+            or out.shape != (n, n_heads * value_dim) \
+            or state.shape[1:] != (n_heads, value_dim, key_dim) \
+            or log_decay.shape != (n, n_heads * key_dim) or log_decay.stride(1) != 1:
+        raise KernelError("delta_rule shapes")
+    if not 1 <= key_dim <= DELTA_CHANNEL_MAX_KEY_DIM:
+        raise KernelError(f"delta_rule with a decay per channel takes key sizes up to "
+                          f"{DELTA_CHANNEL_MAX_KEY_DIM}, got {key_dim}")
+    _check(_load(*delta_rule_library(key_dim)).sllm_delta_rule(
+        _ptr(act), c_int64(act.stride(0)), _ptr(ab), c_int64(ab.stride(0)), c_void_p(0),
+        c_void_p(0), _ptr(state), _ptr(row_start), _ptr(row_slot), _ptr(out), c_int(n_rows),
+        c_int(max_new), c_int(n_heads), c_int(n_kv_heads), c_int(value_dim), _ptr(log_decay),
+        c_int64(log_decay.stride(0)), c_int(b_col), c_int(_code(act.dtype)), _stream()),
+        "delta_rule")
+    return out
+
+
+def lowrank_expand(pre: torch.Tensor, col0: int, w2t: torch.Tensor, out: torch.Tensor,
+                   bias: torch.Tensor | None = None, rate_log: torch.Tensor | None = None,
+                   per_rate: int = 0) -> torch.Tensor:
+    """The second product of a low-rank pair in 32-bit (csrc/recurrent_ops.cu): ``pre`` float32
+    [N, *] holds the hidden values in columns ``[col0, col0 + R)``, ``w2t`` float32 [R, C];
+    ``out`` [N, C] (float32 or bfloat16) gets ``bias + hidden w2t``, or, with ``rate_log``
+    (float32 [C / per_rate]), ``-exp(rate_log[c // per_rate]) * softplus(bias + hidden w2t)``:
+    the logarithm of a decay per channel."""
+    _need(pre, torch.float32, "pre", contiguous=False)
+    _need(w2t, torch.float32, "w2t")
+    _need(out, None, "out")
+    r, c = w2t.shape
+    n = pre.shape[0]
+    if pre.stride(1) != 1 or col0 < 0 or pre.shape[1] < col0 + r or out.shape != (n, c):
+        raise KernelError("lowrank_expand shapes")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+        if bias.numel() != c:
+            raise KernelError("lowrank_expand: one bias per output channel")
+    mode = 0
+    if rate_log is not None:
+        _need(rate_log, torch.float32, "rate_log")
+        if per_rate < 1 or c % per_rate or rate_log.numel() != c // per_rate:
+            raise KernelError("lowrank_expand: one rate per `per_rate` channels")
+        mode = 1
+    _check(_core("sllm_recurrent_ops").sllm_lowrank_expand(
+        _ptr(pre), c_int64(pre.stride(0)), c_int(col0), _ptr(w2t), _ptr(bias), _ptr(rate_log),
+        c_int(per_rate), c_int(mode), _ptr(out), c_int(_code(out.dtype)), c_int(n), c_int(c),
+        c_int(r), _stream()), "lowrank_expand")
     return out
 
 
@@ -1695,3 +1791,93 @@ def concat_cast(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> torch.Te
         _ptr(a), _ptr(b), _ptr(out), c_int(n), c_int(d), c_int(_code(out.dtype)), _stream()),
         "concat_cast")
     return out
+
+
+# ------------------------------------------------------------------------------- layer norm
+
+LAYERNORM_MAX_TERMS = 4
+
+
+def add_layernorm(resid: torch.Tensor, terms: Sequence[tuple[torch.Tensor, float]],
+                  weight: torch.Tensor, bias: torch.Tensor, eps: float, out: torch.Tensor,
+                  out_rows: torch.Tensor | None = None) -> torch.Tensor:
+    """``x = resid + sum(coef * term)`` in 32-bit, then ``out = (x - mean) / sqrt(var + eps) *
+    weight + bias`` (csrc/layer_norm.cu).  Without ``out_rows`` the stream ``resid`` is updated
+    in place and every token is normed; with ``out_rows`` (int32) only those tokens are, and the
+    stream is not written.  ``out`` float32 or bfloat16; it may be ``resid`` itself when there
+    are no terms (the stream normed in place)."""
+    _need(resid, torch.float32, "resid")
+    _need(weight, torch.float32, "weight")
+    _need(bias, torch.float32, "bias")
+    _need(out, None, "out")
+    n, d = resid.shape
+    if len(terms) > LAYERNORM_MAX_TERMS:
+        raise KernelError(f"add_layernorm takes up to {LAYERNORM_MAX_TERMS} terms")
+    term_dtype = out.dtype
+    for i, (t, _) in enumerate(terms):
+        _need(t, None, "term")
+        if t.shape != (n, d):
+            raise KernelError("add_layernorm: a term must have the stream's shape")
+        if i and t.dtype != term_dtype:
+            raise KernelError("add_layernorm: the terms must share a dtype")
+        term_dtype = t.dtype
+    if out is resid and terms:
+        raise KernelError("add_layernorm: the stream is normed in place only without terms")
+    n_out = n if out_rows is None else out_rows.numel()
+    if out_rows is not None:
+        _need(out_rows, torch.int32, "out_rows")
+    if weight.numel() != d or bias.numel() != d or out.shape != (n_out, d):
+        raise KernelError("add_layernorm shapes")
+    ptrs = (c_void_p * LAYERNORM_MAX_TERMS)(*[t.data_ptr() for t, _ in terms])
+    coefs = (c_float * LAYERNORM_MAX_TERMS)(*[float(c) for _, c in terms])
+    _check(_core("sllm_layer_norm").sllm_add_layernorm(
+        _ptr(resid), ptrs, coefs, c_int(len(terms)), c_int(_code(term_dtype)), _ptr(weight),
+        _ptr(bias), c_float(eps), _ptr(out), c_int(_code(out.dtype)), _ptr(out_rows),
+        c_int(n_out), c_int(d), _stream()), "add_layernorm")
+    return out
+
+
+def norm_rope_kv_write(x: torch.Tensor, positions: torch.Tensor, token_row: torch.Tensor,
+                       pages: torch.Tensor, block_table: torch.Tensor, page_size: int,
+                       n_heads: int, n_kv_heads: int, head_dim: int, qk_dim: int, eps: float,
+                       has_kv: bool, write: bool, bias: torch.Tensor | None = None,
+                       q_gain: torch.Tensor | None = None, k_gain: torch.Tensor | None = None,
+                       unit_after: bool = False, cos: torch.Tensor | None = None,
+                       sin: torch.Tensor | None = None, interleaved: bool = True) -> None:
+    """Between an attention mixer's fused projection and its attention kernel
+    (csrc/norm_rope_cache.cu): biases, an RMS norm over all of q (and over all of k) with gains
+    per column, the rotation by the tables' angles, an RMS norm per head without gains
+    (``unit_after``), q back in place and the new keys and values into the pages.  ``x``
+    [N, >= (H + 2 G) * head_dim] (only the H query heads without ``has_kv``); ``qk_dim``: the
+    heads' true size where they are padded up to ``head_dim``."""
+    _need(x, None, "x")
+    _need(positions, torch.int32, "positions")
+    _need(token_row, torch.int32, "token_row")
+    _need(pages, x.dtype, "pages")
+    _need(block_table, torch.int32, "block_table", contiguous=False)
+    cols = (n_heads + (2 * n_kv_heads if has_kv else 0)) * head_dim
+    if x.shape[1] < cols or block_table.stride(1) != 1:
+        raise KernelError("norm_rope_kv_write layout")
+    if pages.shape[1:] != (2, n_kv_heads, page_size, head_dim):
+        raise KernelError(f"pages must be [n_pages, 2, {n_kv_heads}, {page_size}, {head_dim}], "
+                          f"got {list(pages.shape)}")
+    for t, name, size in ((bias, "bias", cols), (q_gain, "q_gain", n_heads * head_dim),
+                          (k_gain, "k_gain", n_kv_heads * head_dim)):
+        if t is not None:
+            _need(t, torch.float32, name)
+            if t.numel() != size:
+                raise KernelError(f"{name} must have {size} entries")
+    rot = 0
+    if cos is not None:
+        _need(cos, torch.float32, "cos")
+        _need(sin, torch.float32, "sin")
+        rot = 2 * cos.shape[1]
+        if sin.shape != cos.shape or not 2 <= rot <= qk_dim:
+            raise KernelError("rotary table width")
+    _check(_core("sllm_norm_rope_cache").sllm_norm_rope_kv_write(
+        _ptr(x), c_int64(x.stride(0)), _ptr(positions), _ptr(token_row), _ptr(bias),
+        _ptr(q_gain), _ptr(k_gain), c_int(int(unit_after)), c_float(eps), c_int(qk_dim),
+        _ptr(cos), _ptr(sin), c_int(rot), c_int(int(interleaved)), _ptr(pages), _ptr(block_table),
+        c_int(block_table.stride(0)), c_int(page_size), c_int(x.shape[0]), c_int(n_heads),
+        c_int(n_kv_heads), c_int(head_dim), c_int(int(has_kv)), c_int(int(write)),
+        c_int(_code(x.dtype)), _stream()), "norm_rope_kv_write")

@@ -1,7 +1,8 @@
 """Parts a layer is put together from: mixer, feed-forward, norm, position encoding, block."""
 
 from . import (attention, biased_attention, block, delta_rule, feed_forward,  # noqa: F401
-               general_delta, latent_attention, norm, position, routed, stream_join,
+               general_delta, latent_attention, norm, normed_attention, position, routed,
+               side_by_side, stream_join,
                token_shift, token_side)  # (registration)
 from .base import (Block, BuildContext, CacheView, FeedForward, KVSpec, Mixer, Norm, Part,
                    PositionEncoding, SideInput, StateSpec, StreamJoin, TokenMix)

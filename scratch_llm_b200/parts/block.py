@@ -13,7 +13,7 @@ import torch
 
 from .base import Block, CacheView, FeedForward, Mixer, Norm, PositionEncoding
 from .registry import register_block
-from .stream import Current, StreamSink
+from .stream import Current, StreamSink, Terms
 
 
 @register_block("pre_norm")
@@ -173,3 +173,34 @@ class SandwichBlock(Block):
             h = self.feed_forward_norm.forward(resid, None)
         self.feed_forward_out_norm.add_normed(resid, self.feed_forward.forward(h))
         return None
+
+
+@register_block("shared_norm")
+class SharedNormBlock(Block):
+    """ONE norm in front of a layer whose branches run side by side on its output:
+    ``h = norm(x)``, ``x <- x + mult * (Mixer(h) + FeedForward(h))`` (the feed-forward is
+    optional).  Nothing is added here: the block hands the branches' outputs on as a weighted sum
+    (:class:`~.stream.Terms`), which the next norm (the next layer's, or the model's last) forms
+    in 32-bit while it reads the stream; so the norm must say ``takes_terms``.  A mixer may
+    itself return such a sum (two mixers side by side, each with a weight)."""
+
+    ROLES = {"mixer": "mixer", "feed_forward": "feed_forward", "norm": "norm",
+             "position": "position"}
+    OPTIONAL_ROLES = frozenset({"feed_forward"})
+    pad_safe = True   # the arrangement itself touches no token: its parts decide
+
+    def __init__(self, mixer: Mixer, norm: Norm, position: PositionEncoding,
+                 feed_forward: FeedForward | None = None, residual_mult: float = 1.0) -> None:
+        if not getattr(norm, "takes_terms", False):
+            raise ValueError("a shared_norm block needs a norm that takes a sum of terms as what "
+                             "is pending (takes_terms)")
+        self.mixer, self.norm, self.position = mixer, norm, position
+        self.feed_forward, self.residual_mult = feed_forward, float(residual_mult)
+
+    def forward(self, resid: torch.Tensor, pending, batch, cache: CacheView, write: bool):
+        h = self.norm.forward(resid, pending)
+        out = Terms.of(self.mixer.forward(h, batch, cache, write, self.position),
+                       self.residual_mult)
+        if self.feed_forward is not None:
+            out = out + Terms.of(self.feed_forward.forward(h), self.residual_mult)
+        return out

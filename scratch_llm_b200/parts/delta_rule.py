@@ -9,6 +9,16 @@
     S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
     out = W_o ( rmsnorm_per_head(o) * gain * silu(W_g x) )
 
+Two options for other designs.  ``decay_rank`` (a number, or -1 for "as the tensors say"): ONE
+DECAY PER KEY CHANNEL instead of one per head, through a low-rank pair of matrices,
+
+    g = exp(-exp(A_log_h) * softplus(W_a2 (W_a1 x) + dt_bias))          laid out heads x key_dim
+
+(``a1`` [rank, d], ``a2`` [H key_dim, rank], ``dt_bias`` [H key_dim]), acting on the rows of S
+that belong to key channels; the second product, softplus and the exponentials are 32-bit.
+``gate_rank`` (likewise): the output gate through a low-rank pair, ``act(W_g2 (W_g1 x))``
+(``g1`` [rank, d], ``g2`` [H value_dim, rank]); ``gate_activation`` "silu" or "sigmoid".
+
 Head h reads key/query head ``h // (n_heads / n_kv_heads)``.  What enters the recurrence (unit
 vectors, gates, decays, the state) is 32-bit; the projections, the convolution and silu run in
 the compute dtype.  The state lives in the cache manager's state slots
@@ -35,25 +45,35 @@ class GatedDeltaRule(Mixer):
 
     def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, key_dim: int,
                  value_dim: int, conv_taps: int, eps: float,
-                 names: Mapping[str, str] | None = None) -> None:
+                 names: Mapping[str, str] | None = None, decay_rank: int | None = None,
+                 gate_rank: int | None = None, gate_activation: str = "silu") -> None:
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads do not group evenly over {n_kv_heads} key heads")
         if not 1 <= key_dim <= ops.DELTA_MAX_KEY_DIM:
             raise ValueError(f"key size {key_dim}: the delta-rule kernel takes 1 to "
                              f"{ops.DELTA_MAX_KEY_DIM}")
+        if decay_rank is not None and key_dim > ops.DELTA_CHANNEL_MAX_KEY_DIM:
+            raise ValueError(f"key size {key_dim}: with a decay per channel the delta-rule kernel "
+                             f"takes up to {ops.DELTA_CHANNEL_MAX_KEY_DIM}")
+        if gate_activation not in ("silu", "sigmoid"):
+            raise ValueError(f"gate_activation must be 'silu' or 'sigmoid', got {gate_activation!r}")
         if not 1 <= conv_taps <= 16:
             raise ValueError(f"the short convolution takes 1 to 16 taps, got {conv_taps}")
         self.hidden_size, self.n_heads, self.n_kv_heads = hidden_size, n_heads, n_kv_heads
         self.key_dim, self.value_dim, self.conv_taps = key_dim, value_dim, conv_taps
         self.eps = float(eps)
+        self.decay_rank, self.gate_rank = decay_rank, gate_rank
+        self.gate_activation = gate_activation
         self.names = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "a": "a", "b": "b",
                       "q_conv": "q.conv", "k_conv": "k.conv", "v_conv": "v.conv",
-                      "A_log": "A_log", "dt_bias": "dt_bias", "norm": "norm", **(names or {})}
+                      "A_log": "A_log", "dt_bias": "dt_bias", "norm": "norm", "a1": "a1",
+                      "a2": "a2", "g1": "g1", "g2": "g2", **(names or {})}
         self.dtype = torch.float32
         self.proj: Linear | None = None     # [q; k; v; g]
         self.ab: Linear | None = None       # [a; b]
         self.o: Linear | None = None
         self.taps = self.taps_t = self.a_log = self.dt_bias = self.gain = None
+        self.a2t = self.g2t = None          # the low-rank pairs' second matrices, [rank, out]
 
     @property
     def conv_channels(self) -> int:
@@ -72,21 +92,46 @@ class GatedDeltaRule(Mixer):
         n, d = self.names, self.hidden_size
         kd, vd = self.n_kv_heads * self.key_dim, self.n_heads * self.value_dim
         K, H = self.conv_taps, self.n_heads
-        return {n["q"]: ParamSpec((kd, d)), n["k"]: ParamSpec((kd, d)), n["v"]: ParamSpec((vd, d)),
-                n["g"]: ParamSpec((vd, d)), n["o"]: ParamSpec((d, vd)),
-                n["a"]: ParamSpec((H, d)), n["b"]: ParamSpec((H, d)),
-                n["q_conv"]: ParamSpec((kd, K), "gain"), n["k_conv"]: ParamSpec((kd, K), "gain"),
-                n["v_conv"]: ParamSpec((vd, K), "gain"), n["A_log"]: ParamSpec((H,), "gain"),
-                n["dt_bias"]: ParamSpec((H,), "gain"),
-                n["norm"]: ParamSpec((self.value_dim,), "gain")}
+        specs = {n["q"]: ParamSpec((kd, d)), n["k"]: ParamSpec((kd, d)), n["v"]: ParamSpec((vd, d)),
+                 n["o"]: ParamSpec((d, vd)), n["b"]: ParamSpec((H, d)),
+                 n["q_conv"]: ParamSpec((kd, K), "gain"), n["k_conv"]: ParamSpec((kd, K), "gain"),
+                 n["v_conv"]: ParamSpec((vd, K), "gain"), n["A_log"]: ParamSpec((H,), "gain"),
+                 n["norm"]: ParamSpec((self.value_dim,), "gain")}
+        if self.decay_rank is None:
+            specs[n["a"]] = ParamSpec((H, d))
+            specs[n["dt_bias"]] = ParamSpec((H,), "gain")
+        else:
+            specs[n["a1"]] = ParamSpec((self.decay_rank, d))
+            specs[n["a2"]] = ParamSpec((H * self.key_dim, self.decay_rank))
+            specs[n["dt_bias"]] = ParamSpec((H * self.key_dim,), "gain")
+        if self.gate_rank is None:
+            specs[n["g"]] = ParamSpec((vd, d))
+        else:
+            specs[n["g1"]] = ParamSpec((self.gate_rank, d))
+            specs[n["g2"]] = ParamSpec((vd, self.gate_rank))
+        return specs
 
     def load(self, tensors: Mapping[str, torch.Tensor], ctx: BuildContext) -> None:
         put = lambda t: t.to(device=ctx.device, dtype=ctx.dtype)  # noqa: E731
         f32 = lambda t: t.to(device=ctx.device, dtype=torch.float32).contiguous()  # noqa: E731
         n = self.names
         self.dtype = ctx.dtype
-        self.proj = Linear(torch.cat([put(tensors[n[k]]) for k in "qkvg"], 0).contiguous())
-        self.ab = Linear(torch.cat([put(tensors[n["a"]]), put(tensors[n["b"]])], 0).contiguous())
+        wide = "qkv" + ("g" if self.gate_rank is None else "")
+        self.proj = Linear(torch.cat([put(tensors[n[k]]) for k in wide], 0).contiguous())
+        # the narrow projections, with a 32-bit output: [a | a1; b; g1]
+        narrow = [tensors[n["a"]] if self.decay_rank is None else tensors[n["a1"]], tensors[n["b"]]]
+        if self.decay_rank is not None:
+            if tensors[n["a1"]].shape[0] != tensors[n["a2"]].shape[1]:
+                raise ValueError("the decay's low-rank matrices do not fit each other")
+            self.decay_rank = tensors[n["a1"]].shape[0]
+            self.a2t = f32(tensors[n["a2"]]).t().contiguous()
+        if self.gate_rank is not None:
+            if tensors[n["g1"]].shape[0] != tensors[n["g2"]].shape[1]:
+                raise ValueError("the gate's low-rank matrices do not fit each other")
+            self.gate_rank = tensors[n["g1"]].shape[0]
+            self.g2t = f32(tensors[n["g2"]]).t().contiguous()
+            narrow.append(tensors[n["g1"]])
+        self.ab = Linear(torch.cat([put(t) for t in narrow], 0).contiguous())
         self.o = Linear(put(tensors[n["o"]]).contiguous())
         self.taps = torch.cat([f32(tensors[n[k]]) for k in ("q_conv", "k_conv", "v_conv")], 0)
         self.taps_t = self.taps.t().contiguous()
@@ -111,8 +156,30 @@ class GatedDeltaRule(Mixer):
         # (padding tokens belong to no row: their read-out stays zero)
         o = (torch.zeros if batch.padded else torch.empty)((n, H * V), dtype=torch.float32,
                                                            device=proj.device)
-        ops.delta_rule(act, ab, self.a_log, self.dt_bias, S, batch.row_start, batch.row_slot, o,
-                       batch.n_rows, H, G, D, V, max_new=1 if batch.n_multi == 0 else 0)
-        out = torch.empty((n, H * V), dtype=proj.dtype, device=proj.device)
-        ops.head_norm_gate(o, proj[:, C:C + H * V], self.gain, self.eps, out, H)
+        max_new = 1 if batch.n_multi == 0 else 0
+        if self.decay_rank is None:
+            ops.delta_rule(act, ab, self.a_log, self.dt_bias, S, batch.row_start, batch.row_slot,
+                           o, batch.n_rows, H, G, D, V, max_new=max_new)
+            b_end = 2 * H
+        else:
+            # the logarithms of the channels' decays, 32-bit from the first product's output on
+            log_decay = torch.empty((n, H * D), dtype=torch.float32, device=proj.device)
+            ops.lowrank_expand(ab, 0, self.a2t, log_decay, bias=self.dt_bias,
+                               rate_log=self.a_log, per_rate=D)
+            ops.delta_rule(act, ab, None, None, S, batch.row_start, batch.row_slot, o,
+                           batch.n_rows, H, G, D, V, max_new=max_new, log_decay=log_decay,
+                           b_col=self.decay_rank)
+            b_end = self.decay_rank + H
+        if self.gate_rank is None:
+            gate = proj[:, C:C + H * V]
+        else:
+            gate = torch.empty((n, H * V), dtype=proj.dtype, device=proj.device)
+            ops.lowrank_expand(ab, b_end, self.g2t, gate)
+        return self._read_out(o, gate)
+
+    def _read_out(self, o: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+        """The heads' read-outs normed and gated, through the output matrix."""
+        out = torch.empty(o.shape, dtype=gate.dtype, device=o.device)
+        ops.head_norm_gate(o, gate, self.gain, self.eps, out, self.n_heads,
+                           gate_activation=self.gate_activation)
         return self.o(out)

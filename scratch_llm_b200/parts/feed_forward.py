@@ -107,3 +107,47 @@ class ActMLP(FeedForward):
     def forward(self, x):
         z = self.up(x)
         return self.down(ops.param_act(z, torch.empty_like(z), self.activation, *self.factors))
+
+
+@register_feed_forward("clamped_glu")
+class ClampedGLU(FeedForward):
+    """A gated feed-forward with clamps: with ``g = min(W_gate x, limit)`` and
+    ``u = clamp(W_up x, -limit, limit)``, ``W_down( g * sigmoid(slope * g) * (u + 1) )``, without
+    biases.  Gate and up are fused into one [2F, d] matrix at load."""
+
+    pad_safe = True   # every token by itself
+
+    def __init__(self, hidden_size: int, intermediate_size: int, limit: float,
+                 slope: float = 1.702, names: Mapping[str, str] | None = None) -> None:
+        if not (limit > 0 and math.isfinite(limit)):
+            raise ValueError(f"limit must be positive, got {limit!r}")
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.limit, self.slope = float(limit), float(slope)
+        self.names = {"gate": "gate", "up": "up", "down": "down", **(names or {})}
+        self.gate_up: Linear | None = None
+        self.down: Linear | None = None
+
+    def kernel_jobs(self, dtype):
+        return [ops.core_job("sllm_stream_ops")]
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        d, f = self.hidden_size, self.intermediate_size
+        return {self.names["gate"]: ParamSpec((f, d)), self.names["up"]: ParamSpec((f, d)),
+                self.names["down"]: ParamSpec((d, f))}
+
+    def load(self, tensors: Mapping[str, torch.Tensor], ctx: BuildContext) -> None:
+        put = lambda t: t.to(device=ctx.device, dtype=ctx.dtype)  # noqa: E731
+        self.gate_up = Linear(torch.cat([put(tensors[self.names["gate"]]),
+                                         put(tensors[self.names["up"]])], 0).contiguous())
+        self.down = Linear(put(tensors[self.names["down"]]).contiguous())
+
+    def activations(self, x, out: torch.Tensor | None = None) -> torch.Tensor:
+        """What the down matrix multiplies, [N, F]; ``out``: where to put it (may be a column
+        slice of a wider buffer)."""
+        z = self.gate_up(x)
+        if out is None:
+            out = torch.empty((z.shape[0], self.intermediate_size), dtype=z.dtype, device=z.device)
+        return ops.clamped_gate(z, out, self.limit, self.slope)
+
+    def forward(self, x):
+        return self.down(self.activations(x))

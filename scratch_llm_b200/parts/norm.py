@@ -15,7 +15,7 @@ from ..kernels import ops
 from ..weights.loader import ParamSpec
 from .base import BuildContext, Norm
 from .registry import register_norm
-from .stream import Current, Normed
+from .stream import Current, Normed, Terms
 
 
 @register_norm("rmsnorm")
@@ -149,3 +149,58 @@ class DynamicTanh(Norm):
 
     def chains_with(self, other) -> bool:
         return isinstance(other, DynamicTanh)
+
+
+@register_norm("layernorm")
+class LayerNorm(Norm):
+    """``(x - mean) / sqrt(var + eps) * w + b`` with the variance as the mean of the squared
+    deviations, all in 32-bit with one rounding at the end.  Tensors below the part's prefix: the
+    gain under ``name`` ("" = the prefix itself) and the offset under ``<name>.b``.
+
+    What is pending for the stream may be a tensor or a weighted sum of several
+    (:class:`~.stream.Terms`): the kernel adds them in while it reads the stream."""
+
+    pad_safe = True       # every token by itself
+    takes_terms = True    # forward() accepts a Terms as what is pending
+
+    def __init__(self, size: int, eps: float, name: str = "") -> None:
+        self.size, self.eps, self.name = size, float(eps), name
+        self.weight: torch.Tensor | None = None
+        self.bias: torch.Tensor | None = None
+        self.dtype = torch.float32
+
+    def _bias_name(self) -> str:
+        return f"{self.name}.b" if self.name else "b"
+
+    def kernel_jobs(self, dtype: torch.dtype):
+        return [ops.core_job("sllm_layer_norm")]
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        return {self.name: ParamSpec((self.size,), "gain"),
+                self._bias_name(): ParamSpec((self.size,), "gain")}
+
+    def load(self, tensors: Mapping[str, torch.Tensor], ctx: BuildContext) -> None:
+        f32 = lambda t: t.to(device=ctx.device, dtype=torch.float32).contiguous()  # noqa: E731
+        self.weight, self.bias = f32(tensors[self.name]), f32(tensors[self._bias_name()])
+        self.dtype = ctx.dtype
+
+    @staticmethod
+    def _terms(delta) -> tuple:
+        if delta is None or isinstance(delta, Current):
+            return ()
+        if isinstance(delta, Terms):
+            return delta.items
+        if isinstance(delta, Normed):
+            raise ValueError("a layer norm's factor is not one number per token: nothing can "
+                             "hand it over")
+        return ((delta, 1.0),)
+
+    def forward(self, resid: torch.Tensor, delta=None, out_rows: torch.Tensor | None = None):
+        n = resid.shape[0] if out_rows is None else out_rows.numel()
+        out = torch.empty((n, self.size), dtype=self.dtype, device=resid.device)
+        return ops.add_layernorm(resid, self._terms(delta), self.weight, self.bias, self.eps,
+                                 out, out_rows)
+
+    def in_place(self, resid: torch.Tensor) -> torch.Tensor:
+        """The stream replaced by its norm (32-bit), as a model does to its embedding output."""
+        return ops.add_layernorm(resid, (), self.weight, self.bias, self.eps, resid)

@@ -13,12 +13,20 @@ rest of the head passes unchanged), and ``scaling_factor`` divides every frequen
 position scaling).  With either, the frequencies ``theta^(-2j / rot_dims) / scaling_factor`` are
 formed in 64-bit and rounded once; the angle ``position * frequency`` is 32-bit arithmetic.
 
+``yarn`` (a mapping ``factor``, ``original``, ``fast``, ``slow``): every frequency f_i is blended
+with ``f_i / factor`` by a ramp over the pair index i.  With ``pair(t) = dims * ln(original /
+(2 pi t)) / (2 ln theta)``, ``lo = max(floor(pair(fast)), 0)`` and ``hi = min(ceil(pair(slow)),
+dims - 1)``, the ramp is ``r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)`` and the frequency
+``f_i / factor * r_i + f_i * (1 - r_i)``; cos and sin are both multiplied by
+``yarn_magnitude * ln(factor) + 1``.
+
 ``none``: no position encoding (a mixer that needs none, or a test part).
 """
 
 from __future__ import annotations
 
-from typing import Mapping
+import math
+from typing import Any, Mapping
 
 import torch
 
@@ -33,7 +41,8 @@ class Rotary(PositionEncoding):
 
     def __init__(self, head_dim: int, theta: float, max_position: int,
                  interleaved: bool = True, rot_dims: int | None = None,
-                 scaling_factor: float = 1.0) -> None:
+                 scaling_factor: float = 1.0, yarn: Mapping[str, Any] | None = None,
+                 yarn_magnitude: float = 0.1) -> None:
         if head_dim % 2:
             raise ValueError(f"rotary positions need an even head size, got {head_dim}")
         if rot_dims is not None and (rot_dims % 2 or not 2 <= rot_dims <= head_dim):
@@ -44,12 +53,38 @@ class Rotary(PositionEncoding):
         self.head_dim, self.theta = head_dim, float(theta)
         self.max_position, self.interleaved = max_position, bool(interleaved)
         self.rot_dims, self.scaling_factor = rot_dims, float(scaling_factor)
+        self.yarn = None if yarn is None else {k: float(yarn[k])
+                                               for k in ("factor", "original", "fast", "slow")}
+        if self.yarn is not None and not (self.yarn["factor"] > 0 and self.yarn["original"] > 0
+                                          and self.yarn["fast"] > 0 and self.yarn["slow"] > 0):
+            raise ValueError(f"yarn scaling needs positive factor, original, fast and slow, "
+                             f"got {yarn!r}")
+        self.yarn_magnitude = float(yarn_magnitude)
         self.cos: torch.Tensor | None = None
         self.sin: torch.Tensor | None = None
 
     def tables(self) -> tuple[torch.Tensor, torch.Tensor]:
         """The table on the CPU in 32-bit: the reference's, or, with ``rot_dims`` or a scaling
         factor, frequencies from 64-bit and 32-bit angles."""
+        if self.yarn is not None:
+            dims = self.rot_dims or self.head_dim
+            y = self.yarn
+
+            def pair(turns: float) -> float:
+                return dims * math.log(y["original"] / (2.0 * math.pi * turns)) \
+                    / (2.0 * math.log(self.theta))
+
+            lo = max(math.floor(pair(y["fast"])), 0)
+            hi = min(math.ceil(pair(y["slow"])), dims - 1)
+            freqs64 = []
+            for j in range(dims // 2):
+                f = self.theta ** (-2.0 * j / dims) / self.scaling_factor
+                ramp = min(max((j - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+                freqs64.append(f / y["factor"] * ramp + f * (1.0 - ramp))
+            inv_freq = torch.tensor(freqs64, dtype=torch.float64).float()
+            freqs = torch.arange(self.max_position).float()[:, None] * inv_freq[None, :]
+            mag = self.yarn_magnitude * math.log(y["factor"]) + 1.0
+            return freqs.cos() * mag, freqs.sin() * mag
         if self.rot_dims is not None or self.scaling_factor != 1.0:
             dims = self.rot_dims or self.head_dim
             inv_freq = torch.tensor([self.theta ** (-2.0 * j / dims) / self.scaling_factor

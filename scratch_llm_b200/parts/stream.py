@@ -55,6 +55,29 @@ class Current:
     x: torch.Tensor
 
 
+@dataclass
+class Terms:
+    """What a layer leaves pending for the stream when it is a weighted sum of several branch
+    outputs: the stream is to receive ``sum(coef * tensor)``.  A norm that takes it
+    (``takes_terms``) forms the sum in 32-bit while it reads the stream, so that neither the
+    sum nor the products by the weights cost a pass or a rounding of their own."""
+
+    items: tuple            # ((tensor [tokens, hidden], coefficient), ...)
+
+    def scaled(self, factor: float) -> "Terms":
+        return Terms(tuple((t, c * factor) for t, c in self.items))
+
+    @staticmethod
+    def of(value, coef: float = 1.0) -> "Terms":
+        """``coef * value`` as terms, whether ``value`` is a tensor or already a sum."""
+        if isinstance(value, Terms):
+            return value.scaled(coef)
+        return Terms(((value, float(coef)),))
+
+    def __add__(self, other: "Terms") -> "Terms":
+        return Terms(self.items + other.items)
+
+
 class StreamSink:
     """Where a branch's last product may put its output: into ``resid``, prepared for ``norm``."""
 
