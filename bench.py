@@ -162,6 +162,39 @@ def titedra_config(name: str):
                    for mlp in (dense, routed, routed, dense)]})
 
 
+def tubevik_config(name: str):
+    """The Tubevik design at the sizes of COMPARE_SIZES: attention (window, cap, gate per head),
+    two mixers side by side (attention in chunks of the window's length with half as many heads
+    beside the delta rule of COMPARE_SIZES with a decay per key channel), attention that borrows
+    the first layer's keys and values, and the two mixers side by side again; every layer with a
+    clamped gated feed-forward of the dense size."""
+    from scratch_llm_b200.config import config_from_dict
+
+    z = COMPARE_SIZES[name]
+    mlp = {"kind": "dense", "ff": z["ff"], "limit": 7.0}
+    rot = {"base": 1000000.0, "dims": z["dim"],
+           "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}
+    attention = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                 "scale": z["dim"] ** -0.5, "softcap": 30.0, "mask": {"size": z["window"]},
+                 "rot": rot}
+    left = {"heads": z["heads"] // 2, "kv_heads": z["kv_heads"] // 2, "dim": z["dim"],
+            "vdim": z["dim"], "scale": 1.0, "mask": {"size": z["window"]},
+            "rot": {"base": 500000.0, "dims": z["dim"] // 2}}
+    both = {"left": left, "right": dict(z["delta"]), "left_scale": 0.8, "right_scale": 1.1}
+    return config_from_dict({
+        "architecture": "Tubevik", "vocab": z["vocab"], "width": z["width"],
+        "norm": {"eps": 1e-5}, "residual_mult": 0.5, "logit_softcap": 30.0, "max_position": 8192,
+        "layers": [{"type": "attention", "mixer": attention, "mlp": mlp},
+                   {"type": "parallel", "mixer": both, "mlp": mlp},
+                   {"type": "attention", "mixer": dict(attention, kv_from=0), "mlp": mlp},
+                   {"type": "parallel", "mixer": both, "mlp": mlp}]})
+
+
+#: low ranks that only a model's tensors say (a size of -1 in a parameter's shape): random
+#: weights are drawn with this one
+RANDOM_LOW_RANK = 64
+
+
 def engine_of(cfg, capacity_tokens: int, max_requests: int, page_size: int):
     """An engine for ``cfg`` with random weights drawn on the device, tensor by tensor."""
     import torch
@@ -182,7 +215,11 @@ def engine_of(cfg, capacity_tokens: int, max_requests: int, page_size: int):
 
     class Lazy(dict):
         def __missing__(self, name):
-            return random_tensors({name: specs[name]}, 0, torch.bfloat16, device=device)[name]
+            spec = specs[name]
+            if -1 in spec.shape:
+                spec = type(spec)(tuple(RANDOM_LOW_RANK if n == -1 else n for n in spec.shape),
+                                  spec.kind)
+            return random_tensors({name: spec}, 0, torch.bfloat16, device=device)[name]
 
     model.load(Lazy(), BuildContext(dtype=torch.bfloat16, device=device))
     model.config = cfg
@@ -191,11 +228,12 @@ def engine_of(cfg, capacity_tokens: int, max_requests: int, page_size: int):
 
 
 def compare_main(args) -> int:
-    """--compare nilevik | vobosun | titedra: prefill and decode throughput of that design beside
+    """--compare nilevik | vobosun | titedra | tubevik: prefill and decode throughput of that design beside
     the engine's other models of equal size (for Vobosun: Nilevik, the closest one, a hybrid of
     attention and a delta rule with normed branch outputs, and the Llama-style model; for
     Titedra: Vobosun, the closest one, with norms around every branch, a partly rotated
-    attention and routed experts, and the Llama-style model), at the sizes of COMPARE_SIZES.
+    attention and routed experts, and the Llama-style model; for Tubevik: Nilevik, the closest one, likewise a hybrid of windowed
+    attention and a gated delta rule, and the Llama-style model), at the sizes of COMPARE_SIZES.
     One JSON line."""
     import torch
 
@@ -214,6 +252,11 @@ def compare_main(args) -> int:
                 entry["vobosun_layers"] = ("attention + dense, general_delta + routed, "
                                            "attention + routed, attention + dense")
                 archs.insert(0, ("vobosun", vobosun_config(name)))
+            if args.compare == "tubevik":
+                entry["tubevik_layers"] = ("attention + dense, (chunked attention | delta rule) "
+                                           "+ dense, attention on the first layer's keys + dense, "
+                                           "(chunked attention | delta rule) + dense")
+                archs.insert(0, ("tubevik", tubevik_config(name)))
             if args.compare == "titedra":
                 entry["titedra_layers"] = ("latent_attention + dense, 2 x (latent_attention + "
                                            "routed) as a loop of one pass, latent_attention + "
@@ -381,7 +424,7 @@ def main() -> int:
                     help="layer sizes (the default is the configuration the metric is quoted on)")
     ap.add_argument("--serve", type=int, default=0, metavar="N",
                     help="also run the continuous-batching workload with N requests")
-    ap.add_argument("--compare", default=None, choices=["nilevik", "vobosun", "titedra"],
+    ap.add_argument("--compare", default=None, choices=["nilevik", "vobosun", "titedra", "tubevik"],
                     help="instead of the headline workload: prefill and decode throughput of "
                          "this design beside the Llama-style model of equal size")
     ap.add_argument("--compare-sizes", default=None, choices=sorted(COMPARE_SIZES),

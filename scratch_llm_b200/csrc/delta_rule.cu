@@ -47,6 +47,9 @@
 // pair of tokens, shared by the CTA's 16 columns.  The step size then comes from column b_col +
 // head of `ab`, and A_log / dt_bias are the caller's business (they are inside log_decay).
 //
+// The weights depend on keys, queries and decays alone: delta_weights_kernel forms the tables of
+// ALL chunks of a step in parallel before the scan starts, which then reads its chunk's table.
+//
 // Compiled once per key size: -DSLLM_HEAD_DIM=<D>.
 #include "common.cuh"
 
@@ -76,6 +79,10 @@ struct DeltaArgs {
     // a decay per key channel: [tokens, >= H * D] logarithms (null: one decay per head from a)
     const float* log_decay; int64_t ld_decay;
     int b_col;                           // the step input of head h is ab[b_col + h]
+    // with a decay per channel: the chunks' tables of weights, made by delta_weights_kernel before
+    // this launch (null: every CTA forms its chunk's table itself).  The chunk that starts at
+    // token t of row r has slot t / TC + r; a slot holds [H][2 TC][TC] floats.
+    const float* tables;
 };
 // the kernel for a decay per channel stages a third [TC][D] table in (static) shared memory
 constexpr bool CHANNEL_FITS = D <= 192;
@@ -360,7 +367,9 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(const DeltaArgs a) 
             const bool with_q = row >= TC;
             float dot = 0.f;
             const bool used = t < nt && s < nt && (with_q ? s <= t : s < t);
-            if (used && CHANNEL) {
+            if (CHANNEL && a.tables != nullptr) {
+                dot = a.tables[((((int64_t)(t0 + c0) / TC + r) * a.H + head) * 2 * TC + row) * TC + s];
+            } else if (used && CHANNEL) {
                 const float* x = with_q ? &qs[t][0] : &ks[t][0];
                 for (int e = 0; e < D; ++e)
                     dot = fmaf(x[e] * ks[s][e], expf(lam[t][e] - lam[s][e]), dot);
@@ -479,6 +488,87 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(const DeltaArgs a) 
     }
 }
 
+// The tables of weights of all chunks of a step at once, for a decay per channel (the comment at
+// the top): they depend on the keys, queries and decays alone, not on the state, so the chunks of
+// a row need not wait for each other.  grid (chunks of the longest row, H, rows), 256 threads: a
+// thread per pair of tokens that the table uses (120 pairs of keys with earlier keys, 136 of
+// queries with keys up to their own).  tables: [slots][H][2 TC][TC] as DeltaArgs says; entries
+// that no pair uses are zero.
+constexpr int TABLE_THREADS = 256;
+template <typename T>
+__global__ void __launch_bounds__(TABLE_THREADS) delta_weights_kernel(const DeltaArgs a, float* tables) {
+    __shared__ __align__(16) float ks[TC][LDK];
+    __shared__ __align__(16) float qs[TC][LDK];
+    __shared__ __align__(16) float lam[TC][LDK];
+    pdl_wait();
+    pdl_trigger();
+    const int r = blockIdx.z, head = blockIdx.y, c0 = blockIdx.x * TC;
+    const int t0 = a.row_start[r], n_new = a.row_start[r + 1] - t0;
+    if (c0 >= n_new || n_new <= 1) return;     // (rows of one token take the kernel's plain path)
+    const int nt = min(TC, n_new - c0);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = head / (a.H / a.G);
+    const T* act = reinterpret_cast<const T*>(a.act);
+    const int64_t k_col0 = (int64_t)a.G * D;
+    for (int idx = tid; idx < TC * D; idx += TABLE_THREADS) {
+        const int t = idx / D, e = idx - t * D;
+        float k = 0.f, q = 0.f, l = 0.f;
+        if (t < nt) {
+            const T* row = act + (int64_t)(t0 + c0 + t) * a.ld_act + (int64_t)g * D;
+            q = to_float(row[e]);
+            k = to_float(row[k_col0 + e]);
+            l = a.log_decay[(int64_t)(t0 + c0 + t) * a.ld_decay + (int64_t)head * D + e];
+        }
+        ks[t][e] = k; qs[t][e] = q; lam[t][e] = l;
+    }
+    __syncthreads();
+    const float q_scale = rsqrtf((float)D);
+    for (int t = warp; t < nt; t += TABLE_THREADS / 32) {
+        float sk = 0.f, sq = 0.f;
+        for (int e = lane; e < D; e += 32) {
+            sk += ks[t][e] * ks[t][e];
+            sq += qs[t][e] * qs[t][e];
+        }
+        sk = warp_sum(sk);
+        sq = warp_sum(sq);
+        const float ik = 1.0f / sqrtf(sk + 1e-6f), iq = q_scale / sqrtf(sq + 1e-6f);
+        for (int e = lane; e < D; e += 32) {
+            ks[t][e] *= ik;
+            qs[t][e] *= iq;
+        }
+    }
+    for (int e = tid; e < D; e += TABLE_THREADS) {
+        float c = 0.f;
+#pragma unroll
+        for (int t = 0; t < TC; ++t) {
+            c += lam[t][e];
+            lam[t][e] = c;
+        }
+    }
+    __syncthreads();
+    float* table = tables + (((int64_t)(t0 + c0) / TC + r) * a.H + head) * 2 * TC * TC;
+    // thread -> pair: the first 120 threads take (t, s < t) of keys with keys, the other 136 take
+    // (t, s <= t) of queries with keys; both triangles are walked row by row
+    const bool with_q = tid >= TC * (TC - 1) / 2;
+    int p = with_q ? tid - TC * (TC - 1) / 2 : tid, t = 0;
+    if (with_q) { while (p > t) { p -= t + 1; ++t; } }        // row t has t + 1 pairs
+    else { t = 1; while (p >= t) { p -= t; ++t; } }           // row t has t pairs
+    const int sidx = p;
+    float dot = 0.f;
+    if (t < nt) {
+        const float* x = with_q ? &qs[t][0] : &ks[t][0];
+#pragma unroll 4
+        for (int e = 0; e < D; ++e)
+            dot = fmaf(x[e] * ks[sidx][e], __expf(lam[t][e] - lam[sidx][e]), dot);
+    }
+    table[((with_q ? TC : 0) + t) * TC + sidx] = dot;
+    // the entries that no pair uses
+    for (int idx = tid; idx < 2 * TC * TC; idx += TABLE_THREADS) {
+        const int row = idx / TC, s2 = idx - row * TC, t2 = row & (TC - 1);
+        if (row >= TC ? s2 > t2 : s2 >= t2) table[idx] = 0.f;
+    }
+}
+
 }  // namespace sllm
 
 using namespace sllm;
@@ -492,7 +582,8 @@ SLLM_EXPORT int sllm_delta_rule(const void* act, int64_t ld_act, const float* ab
                                 const float* A_log, const float* dt_bias, float* state,
                                 const int* row_start, const int* row_slot, float* out, int n_rows,
                                 int max_new, int H, int G, int V, const float* log_decay,
-                                int64_t ld_decay, int b_col, int dtype, cudaStream_t stream) {
+                                int64_t ld_decay, int b_col, float* tables, int longest,
+                                int dtype, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G != 0 || V <= 0 || n_rows > 65535 || H > 65535 ||
         ld_act < 2 * (int64_t)G * D + (int64_t)H * V || b_col < 0 || ld_ab < b_col + H ||
@@ -501,6 +592,7 @@ SLLM_EXPORT int sllm_delta_rule(const void* act, int64_t ld_act, const float* ab
         return (int)cudaErrorInvalidValue;
     DeltaArgs a;
     a.log_decay = log_decay; a.ld_decay = ld_decay; a.b_col = b_col;
+    a.tables = nullptr;
     a.act = act; a.ld_act = ld_act; a.ab = ab; a.ld_ab = ld_ab; a.A_log = A_log;
     a.dt_bias = dt_bias; a.state = state; a.row_start = row_start; a.row_slot = row_slot;
     a.out = out; a.H = H; a.G = G; a.V = V;
@@ -526,6 +618,16 @@ SLLM_EXPORT int sllm_delta_rule(const void* act, int64_t ld_act, const float* ab
     if (dtype != 0 && dtype != 1) return (int)cudaErrorInvalidValue;
     if (log_decay) {
         if constexpr (CHANNEL_FITS) {
+            if (tables != nullptr && longest > 1) {
+                // all chunks' tables at once; `tables` holds (tokens / TC + n_rows + 1) slots of
+                // H * 2 TC * TC floats, `longest` is the most tokens any row brings
+                dim3 tgrid((longest + TC - 1) / TC, H, n_rows);
+                if (tgrid.x > 65535u * 32u) return (int)cudaErrorInvalidValue;
+                if (dtype == 0) delta_weights_kernel<float><<<tgrid, TABLE_THREADS, 0, stream>>>(a, tables);
+                else delta_weights_kernel<__nv_bfloat16><<<tgrid, TABLE_THREADS, 0, stream>>>(a, tables);
+                SLLM_LAUNCH_CHECK();
+                a.tables = tables;
+            }
             if (dtype == 0) {
                 if (vector) delta_rule_kernel<float, (D % 4 == 0), true><<<grid, THREADS, 0, stream>>>(a);
                 else delta_rule_kernel<float, false, true><<<grid, THREADS, 0, stream>>>(a);

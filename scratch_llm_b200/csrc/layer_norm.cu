@@ -58,6 +58,64 @@ add_layernorm_kernel(float* resid, const LnTerms terms, const float* __restrict_
         o[c] = from_float<TO>((row[c] - mean) * inv * w[c] + b[c]);
 }
 
+// Four elements at a time (d a multiple of 4, every base 16-byte aligned): the same sums in
+// another order.
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+    return make_float4(__low2float(h[0]), __high2float(h[0]), __low2float(h[1]), __high2float(h[1]));
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+    uint2 r;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+    h[0] = __floats2bfloat162_rn(v.x, v.y);
+    h[1] = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(p) = r;
+}
+
+template <typename TD, typename TO>
+__global__ void __launch_bounds__(LN_THREADS)
+add_layernorm_vec_kernel(float* resid, const LnTerms terms, const float* __restrict__ w,
+                         const float* __restrict__ b, float eps, TO* out,
+                         const int* __restrict__ out_rows, int d) {
+    extern __shared__ __align__(16) float row[];      // [d]
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_trigger();
+    const int64_t n = out_rows ? out_rows[blockIdx.x] : blockIdx.x;
+    float* r = resid + n * d;
+    float sum = 0.f;
+    for (int c = threadIdx.x * 4; c < d; c += LN_THREADS * 4) {
+        float4 x = load4(r + c);
+#pragma unroll
+        for (int i = 0; i < LN_MAX_TERMS; ++i)
+            if (i < terms.n) {
+                const float4 t = load4(reinterpret_cast<const TD*>(terms.p[i]) + n * d + c);
+                x.x = fmaf(terms.coef[i], t.x, x.x); x.y = fmaf(terms.coef[i], t.y, x.y);
+                x.z = fmaf(terms.coef[i], t.z, x.z); x.w = fmaf(terms.coef[i], t.w, x.w);
+            }
+        if (terms.n > 0 && out_rows == nullptr) store4(r + c, x);
+        store4(row + c, x);
+        sum += (x.x + x.y) + (x.z + x.w);
+    }
+    const float mean = block_sum(sum, scratch) / (float)d;
+    float dev = 0.f;
+    for (int c = threadIdx.x * 4; c < d; c += LN_THREADS * 4) {
+        const float4 x = load4(row + c);
+        const float e0 = x.x - mean, e1 = x.y - mean, e2 = x.z - mean, e3 = x.w - mean;
+        dev += (e0 * e0 + e1 * e1) + (e2 * e2 + e3 * e3);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(dev, scratch) / (float)d + eps);
+    TO* o = out + (int64_t)blockIdx.x * d;
+    for (int c = threadIdx.x * 4; c < d; c += LN_THREADS * 4) {
+        const float4 x = load4(row + c), g = load4(w + c), h = load4(b + c);
+        store4(o + c, make_float4((x.x - mean) * inv * g.x + h.x, (x.y - mean) * inv * g.y + h.y,
+                                  (x.z - mean) * inv * g.z + h.z, (x.w - mean) * inv * g.w + h.w));
+    }
+}
+
 }  // namespace sllm
 
 using namespace sllm;
@@ -80,6 +138,8 @@ SLLM_EXPORT int sllm_add_layernorm(float* resid, const void* const* term_ptrs,
         t.coef[i] = i < n_terms ? term_coefs[i] : 0.f;
     }
     const size_t smem = (size_t)d * sizeof(float);
+    bool vec = d % 4 == 0 && !(((uintptr_t)resid | (uintptr_t)w | (uintptr_t)b | (uintptr_t)out) & 15);
+    for (int i = 0; i < n_terms; ++i) vec = vec && !((uintptr_t)term_ptrs[i] & 15);
 #define SLLM_LN_LAUNCH(TD, TO)                                                                  \
     do {                                                                                        \
         if (smem > 48 * 1024) {                                                                 \
@@ -87,6 +147,13 @@ SLLM_EXPORT int sllm_add_layernorm(float* resid, const void* const* term_ptrs,
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize,   \
                                                  (int)smem);                                    \
             if (e != cudaSuccess) return (int)e;                                                \
+        }                                                                                       \
+        if (vec && smem <= 48 * 1024) {                                                         \
+            cudaError_t e = sllm_launch_pdl(add_layernorm_vec_kernel<TD, TO>, dim3(n_out),      \
+                                            dim3(LN_THREADS), smem, stream, resid, t, w, b,     \
+                                            eps, (TO*)out, out_rows, d);                        \
+            if (e != cudaSuccess) return (int)e;                                                \
+            break;                                                                              \
         }                                                                                       \
         cudaError_t e = sllm_launch_pdl(add_layernorm_kernel<TD, TO>, dim3(n_out),              \
                                         dim3(LN_THREADS), smem, stream, resid, t, w, b, eps,    \

@@ -120,13 +120,13 @@ __global__ void conv_state_update_kernel(const T* __restrict__ x, int64_t ldx, i
 }
 
 // grid (tokens, ceil(H / 4)); one warp per (token, head).  o: [n_tokens, H * V] float;
-// gate: rows ldg apart; out: [n_tokens, H * V].  gain has V entries (every head the same) or,
+// gate: rows ldg apart; out: rows ldo apart (a column slice of a wider buffer, or H * V).  gain has V entries (every head the same) or,
 // with gain_per_head, H * V.  gate_act: 0 = silu(gate), 1 = sigmoid(gate).
 template <typename T>
 __global__ void __launch_bounds__(128)
 head_norm_gate_kernel(const float* __restrict__ o, const T* __restrict__ gate, int64_t ldg,
-                      const float* __restrict__ gain, float eps, T* __restrict__ out, int H,
-                      int V, int gain_per_head, int gate_act) {
+                      const float* __restrict__ gain, float eps, T* __restrict__ out, int64_t ldo,
+                      int H, int V, int gain_per_head, int gate_act) {
     pdl_wait();
     pdl_trigger();
     const int64_t n = blockIdx.x;
@@ -139,7 +139,7 @@ head_norm_gate_kernel(const float* __restrict__ o, const T* __restrict__ gate, i
     const float inv = 1.0f / sqrtf(ss / (float)V + eps);
     const T* g = gate + n * ldg + (int64_t)head * V;
     const float* gn = gain + (gain_per_head ? (int64_t)head * V : 0);
-    T* dst = out + (n * H + head) * V;
+    T* dst = out + n * ldo + (int64_t)head * V;
     for (int j = lane; j < V; j += 32) {
         const float z = to_float(g[j]);
         const float sig = 1.0f / (1.0f + expf(-z));
@@ -319,19 +319,20 @@ SLLM_EXPORT int sllm_conv_state_update(const void* x, int64_t ldx, int K, void* 
 }
 
 SLLM_EXPORT int sllm_head_norm_gate(const float* o, const void* gate, int64_t ldg,
-                                    const float* gain, float eps, void* out, int n_tokens, int H,
-                                    int V, int gain_per_head, int gate_act, int dtype,
-                                    cudaStream_t stream) {
+                                    const float* gain, float eps, void* out, int64_t ldo,
+                                    int n_tokens, int H, int V, int gain_per_head, int gate_act,
+                                    int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (H <= 0 || V <= 0 || gate_act < 0 || gate_act > 1) return (int)cudaErrorInvalidValue;
+    if (H <= 0 || V <= 0 || gate_act < 0 || gate_act > 1 || ldo < (int64_t)H * V)
+        return (int)cudaErrorInvalidValue;
     dim3 grid(n_tokens, (H + 3) / 4);
     if (dtype == 0)
         head_norm_gate_kernel<float><<<grid, 128, 0, stream>>>(o, (const float*)gate, ldg, gain,
-                                                               eps, (float*)out, H, V,
+                                                               eps, (float*)out, ldo, H, V,
                                                                gain_per_head, gate_act);
     else if (dtype == 1)
         head_norm_gate_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(
-            o, (const __nv_bfloat16*)gate, ldg, gain, eps, (__nv_bfloat16*)out, H, V,
+            o, (const __nv_bfloat16*)gate, ldg, gain, eps, (__nv_bfloat16*)out, ldo, H, V,
             gain_per_head, gate_act);
     else
         return (int)cudaErrorInvalidValue;

@@ -1158,17 +1158,18 @@ def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, gain: torch.Tensor, eps:
                    out: torch.Tensor, n_heads: int, gate_activation: str = "silu") -> torch.Tensor:
     """out[n, h, :] = o[n, h, :] / sqrt(mean(o[n, h, :]^2) + eps) * gain * act(gate[n, h, :]);
     ``o`` float32 [N, H * V], ``gate`` [N, H * V] (may be a column slice), ``gain`` float32 [V]
-    (the same for every head) or [H * V]; ``gate_activation``: "silu" or "sigmoid"."""
+    (the same for every head) or [H * V]; ``gate_activation``: "silu" or "sigmoid".  ``out`` may
+    be a column slice of a wider buffer."""
     _need(o, torch.float32, "o")
     _need(gate, out.dtype, "gate", contiguous=False)
     _need(gain, torch.float32, "gain")
-    _need(out, None, "out")
+    _need(out, None, "out", contiguous=False)
     n, hv = o.shape
     if hv % n_heads or gain.numel() not in (hv, hv // n_heads):
         raise KernelError("head_norm_gate: the gain has one entry per channel of a head, or of all")
     v = hv // n_heads
     per_head = gain.numel() == hv and n_heads > 1
-    if gate.shape != (n, hv) or out.shape != (n, hv) or gate.stride(1) != 1:
+    if gate.shape != (n, hv) or out.shape != (n, hv) or gate.stride(1) != 1 or out.stride(1) != 1:
         raise KernelError("head_norm_gate shapes")
     try:
         act = {"silu": 0, "sigmoid": 1}[gate_activation]
@@ -1176,7 +1177,7 @@ def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, gain: torch.Tensor, eps:
         raise KernelError(f"unknown gate activation {gate_activation!r}") from None
     _check(_core("sllm_recurrent_ops").sllm_head_norm_gate(
         _ptr(o), _ptr(gate), c_int64(gate.stride(0)), _ptr(gain), c_float(eps), _ptr(out),
-        c_int(n), c_int(n_heads), c_int(v), c_int(int(per_head)), c_int(act),
+        c_int64(out.stride(0)), c_int(n), c_int(n_heads), c_int(v), c_int(int(per_head)), c_int(act),
         c_int(_code(out.dtype)), _stream()), "head_norm_gate")
     return out
 
@@ -1517,7 +1518,7 @@ def delta_rule(act: torch.Tensor, ab: torch.Tensor, a_log: torch.Tensor, dt_bias
                state: torch.Tensor, row_start: torch.Tensor, row_slot: torch.Tensor,
                out: torch.Tensor, n_rows: int, n_heads: int, n_kv_heads: int, key_dim: int,
                value_dim: int, max_new: int = 0, log_decay: torch.Tensor | None = None,
-               b_col: int | None = None) -> torch.Tensor:
+               b_col: int | None = None, longest: int = 0) -> torch.Tensor:
     """The gated delta rule over the packed batch (csrc/delta_rule.cu): ``act`` [N, 2 G D + H V]
     holds query heads, key heads and value heads after the convolution; ``ab`` float32
     [N, 2 H] the decay and step inputs; ``state`` float32 [slots, H, V, D] is read and written
@@ -1526,13 +1527,15 @@ def delta_rule(act: torch.Tensor, ab: torch.Tensor, a_log: torch.Tensor, dt_bias
 
     ``log_decay`` (float32 [N, H * D], at most 0): a decay per key CHANNEL, given as its
     logarithm; ``a_log`` and ``dt_bias`` are then not read (may be None), and head h's step input
-    is column ``b_col + h`` of ``ab`` (any width)."""
+    is column ``b_col + h`` of ``ab`` (any width).  ``longest``: the most tokens any row brings,
+    if known and above 1: the chunks' tables of weights are then all formed at once by a kernel
+    of their own before the scan (0: every CTA of the scan forms its own)."""
     _need(act, None, "act", contiguous=False)
     _need(ab, torch.float32, "ab", contiguous=False)
     if log_decay is not None:
         return _delta_rule_channels(act, ab, state, row_start, row_slot, out, n_rows, n_heads,
                                     n_kv_heads, key_dim, value_dim, max_new, log_decay,
-                                    n_heads if b_col is None else b_col)
+                                    n_heads if b_col is None else b_col, longest)
     _need(a_log, torch.float32, "A_log")
     _need(dt_bias, torch.float32, "dt_bias")
     _need(state, torch.float32, "state")
@@ -1552,7 +1555,7 @@ def delta_rule(act: torch.Tensor, ab: torch.Tensor, a_log: torch.Tensor, dt_bias
         _ptr(act), c_int64(act.stride(0)), _ptr(ab), c_int64(ab.stride(0)), _ptr(a_log),
         _ptr(dt_bias), _ptr(state), _ptr(row_start), _ptr(row_slot), _ptr(out), c_int(n_rows),
         c_int(max_new), c_int(n_heads), c_int(n_kv_heads), c_int(value_dim), c_void_p(0),
-        c_int64(0), c_int(n_heads), c_int(_code(act.dtype)), _stream()),
+        c_int64(0), c_int(n_heads), c_void_p(0), c_int(0), c_int(_code(act.dtype)), _stream()),
         "delta_rule")
     return out
 
@@ -1561,8 +1564,12 @@ def delta_rule(act: torch.Tensor, ab: torch.Tensor, a_log: torch.Tensor, dt_bias
 DELTA_CHANNEL_MAX_KEY_DIM = 192
 
 
+#: tokens per chunk of the delta-rule kernel (a table of weights per chunk and head)
+DELTA_CHUNK = 16
+
+
 def _delta_rule_channels(act, ab, state, row_start, row_slot, out, n_rows, n_heads, n_kv_heads,
-                         key_dim, value_dim, max_new, log_decay, b_col) -> torch.Tensor:
+                         key_dim, value_dim, max_new, log_decay, b_col, longest) -> torch.Tensor:
     _need(log_decay, torch.float32, "log_decay", contiguous=False)
     _need(state, torch.float32, "state")
     _need(row_start, torch.int32, "row_start")
@@ -1579,11 +1586,17 @@ def _delta_rule_channels(act, ab, state, row_start, row_slot, out, n_rows, n_hea
     if not 1 <= key_dim <= DELTA_CHANNEL_MAX_KEY_DIM:
         raise KernelError(f"delta_rule with a decay per channel takes key sizes up to "
                           f"{DELTA_CHANNEL_MAX_KEY_DIM}, got {key_dim}")
+    tables = None
+    if longest > 1 and max_new != 1:
+        slots = n // DELTA_CHUNK + n_rows + 1
+        tables = torch.empty((slots, n_heads, 2 * DELTA_CHUNK, DELTA_CHUNK), dtype=torch.float32,
+                             device=act.device)
     _check(_load(*delta_rule_library(key_dim)).sllm_delta_rule(
         _ptr(act), c_int64(act.stride(0)), _ptr(ab), c_int64(ab.stride(0)), c_void_p(0),
         c_void_p(0), _ptr(state), _ptr(row_start), _ptr(row_slot), _ptr(out), c_int(n_rows),
         c_int(max_new), c_int(n_heads), c_int(n_kv_heads), c_int(value_dim), _ptr(log_decay),
-        c_int64(log_decay.stride(0)), c_int(b_col), c_int(_code(act.dtype)), _stream()),
+        c_int64(log_decay.stride(0)), c_int(b_col), _ptr(tables), c_int(longest),
+        c_int(_code(act.dtype)), _stream()),
         "delta_rule")
     return out
 

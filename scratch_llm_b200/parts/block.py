@@ -12,6 +12,7 @@ from __future__ import annotations
 import torch
 
 from .base import Block, CacheView, FeedForward, Mixer, Norm, PositionEncoding
+from .linear import Linear
 from .registry import register_block
 from .stream import Current, StreamSink, Terms
 
@@ -196,9 +197,54 @@ class SharedNormBlock(Block):
                              "is pending (takes_terms)")
         self.mixer, self.norm, self.position = mixer, norm, position
         self.feed_forward, self.residual_mult = feed_forward, float(residual_mult)
+        #: the branches' output matrices joined into one [hidden, sum of their inputs], once the
+        #: weights are there: None = not tried yet, False = a branch cannot hand out its activations
+        self._joint = None
+        self._widths: list[tuple[int, int]] = []     # per segment: (first column, width)
+        self._zero_fill = False
+
+    def _join_outputs(self) -> None:
+        """Both branches end with a matrix product into the stream, weighted by constants:
+        ``sum_i c_i W_i a_i = [c_1 W_1 | c_2 W_2 | ...] [a_1; a_2; ...]``, one product over the
+        concatenated activations, which the branches write side by side into one buffer.  The
+        constants go into the joined matrix (formed in 32-bit, rounded once)."""
+        branches = [self.mixer] + ([self.feed_forward] if self.feed_forward is not None else [])
+        segments = []
+        for part in branches:
+            mine = part.out_segments() if hasattr(part, "out_segments") else None
+            if mine is None:
+                self._joint = False
+                return
+            segments += mine
+        blocks, at = [], 0
+        for w, coef in segments:
+            width = w.shape[1]
+            padded = -(-width // 8) * 8        # every segment starts on a 16-byte boundary
+            block = w.new_zeros((w.shape[0], padded))
+            block[:, :width] = (w.float() * coef).to(w.dtype) if coef != 1.0 else w
+            blocks.append(block)
+            self._widths.append((at, width))
+            self._zero_fill |= padded != width
+            at += padded
+        self._n_mixer = len(segments) - (1 if self.feed_forward is not None else 0)
+        self._joint = Linear(torch.cat(blocks, 1).contiguous())
+        for part in branches:
+            part.release_out()
 
     def forward(self, resid: torch.Tensor, pending, batch, cache: CacheView, write: bool):
         h = self.norm.forward(resid, pending)
+        if self._joint is None:
+            self._join_outputs()
+        if self._joint is not False:
+            w = self._joint.weight
+            cat = (torch.zeros if self._zero_fill else torch.empty)(
+                (h.shape[0], w.shape[1]), dtype=w.dtype, device=w.device)
+            outs = [cat[:, a:a + n] for a, n in self._widths]
+            self.mixer.activations_into(h, batch, cache, write, self.position,
+                                        outs[:self._n_mixer])
+            if self.feed_forward is not None:
+                self.feed_forward.activations_into(h, outs[self._n_mixer:])
+            return Terms.of(self._joint(cat), self.residual_mult)
         out = Terms.of(self.mixer.forward(h, batch, cache, write, self.position),
                        self.residual_mult)
         if self.feed_forward is not None:

@@ -139,6 +139,12 @@ class GatedDeltaRule(Mixer):
         self.gain = f32(tensors[n["norm"]])
 
     def forward(self, x, batch, cache: CacheView, write: bool, position: PositionEncoding):
+        return self.o(self.heads_out(x, batch, cache, write, position))
+
+    def heads_out(self, x, batch, cache: CacheView, write: bool, position: PositionEncoding,
+                  out: torch.Tensor | None = None) -> torch.Tensor:
+        """The heads' read-outs, normed and gated [N, H * value_dim]: what the output matrix
+        multiplies.  ``out``: where to put them (may be a column slice)."""
         H, G, D, V, K = self.n_heads, self.n_kv_heads, self.key_dim, self.value_dim, self.conv_taps
         C = self.conv_channels
         state = cache.state if isinstance(cache.state, tuple) else (cache.state, None)
@@ -168,18 +174,27 @@ class GatedDeltaRule(Mixer):
                                rate_log=self.a_log, per_rate=D)
             ops.delta_rule(act, ab, None, None, S, batch.row_start, batch.row_slot, o,
                            batch.n_rows, H, G, D, V, max_new=max_new, log_decay=log_decay,
-                           b_col=self.decay_rank)
+                           b_col=self.decay_rank, longest=batch.max_new)
             b_end = self.decay_rank + H
         if self.gate_rank is None:
             gate = proj[:, C:C + H * V]
         else:
             gate = torch.empty((n, H * V), dtype=proj.dtype, device=proj.device)
             ops.lowrank_expand(ab, b_end, self.g2t, gate)
-        return self._read_out(o, gate)
-
-    def _read_out(self, o: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
-        """The heads' read-outs normed and gated, through the output matrix."""
-        out = torch.empty(o.shape, dtype=gate.dtype, device=o.device)
+        if out is None:
+            out = torch.empty(o.shape, dtype=gate.dtype, device=o.device)
         ops.head_norm_gate(o, gate, self.gain, self.eps, out, self.n_heads,
                            gate_activation=self.gate_activation)
-        return self.o(out)
+        return out
+
+    # -- for a block that multiplies several branches' activations by one joined output matrix
+
+    def out_segments(self):
+        """[(the output matrix [hidden, H * value_dim], its weight in the layer's sum)]."""
+        return [(self.o.weight, 1.0)]
+
+    def release_out(self) -> None:
+        self.o = None
+
+    def activations_into(self, x, batch, cache: CacheView, write: bool, position, outs) -> None:
+        self.heads_out(x, batch, cache, write, position, out=outs[0])

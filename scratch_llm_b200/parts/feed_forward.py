@@ -151,3 +151,14 @@ class ClampedGLU(FeedForward):
 
     def forward(self, x):
         return self.down(self.activations(x))
+
+    # -- for a block that multiplies several branches' activations by one joined output matrix
+
+    def out_segments(self):
+        return [(self.down.weight, 1.0)]
+
+    def release_out(self) -> None:
+        self.down = None
+
+    def activations_into(self, x, outs) -> None:
+        self.activations(x, out=outs[0])

@@ -222,3 +222,15 @@ class NormedAttention(Mixer):
                               self.window, split=True, n_splits=n_splits, scratch=scratch,
                               sinks=self.sinks, softcap=self.softcap, chunk=self.chunk,
                               merge_inside=ctas <= ops.attention_decode_slots(hd))
+
+    # -- for a block that multiplies several branches' activations by one joined output matrix
+
+    def out_segments(self):
+        """[(the output matrix [hidden, H * head_dim], its weight in the layer's sum)]."""
+        return [(self.o.weight, 1.0)]
+
+    def release_out(self) -> None:
+        self.o = None
+
+    def activations_into(self, x, batch, cache: CacheView, write: bool, position, outs) -> None:
+        self.heads_out(x, batch, cache, write, position, out=outs[0])

@@ -113,3 +113,28 @@ class SideBySide(Mixer):
             term = Terms.of(side.forward(x, batch, view, write, position), scale)
             out = term if out is None else out + term
         return out
+
+    # -- for a block that multiplies several branches' activations by one joined output matrix
+
+    def out_segments(self):
+        """Both sides' output matrices, each with its side's weight in the sum; None if a side
+        cannot hand out its activations."""
+        segments = []
+        for side, scale in zip(self.sides, self.scales):
+            if not hasattr(side, "out_segments"):
+                return None
+            mine = side.out_segments()
+            if mine is None:
+                return None
+            if len(mine) != 1:
+                return None
+            segments += [(w, c * scale) for w, c in mine]
+        return segments
+
+    def release_out(self) -> None:
+        for side in self.sides:
+            side.release_out()
+
+    def activations_into(self, x, batch, cache: CacheView, write: bool, position, outs) -> None:
+        for i, (side, view) in enumerate(zip(self.sides, self._views(cache))):
+            side.activations_into(x, batch, view, write, position, outs[i:i + 1])

@@ -295,7 +295,7 @@ def test_delta_rule_with_a_decay_per_channel(H, G, D, V, dtype):
     slots = [2, 0]
     tol = dict(rtol=2e-4, atol=2e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-3)
 
-    def run(cuts):
+    def run(cuts, tables=False):
         state[slots] = 0.0
         got = [[], []]
         at = 0
@@ -307,16 +307,20 @@ def test_delta_rule_with_a_decay_per_channel(H, G, D, V, dtype):
             n = act.shape[0] // 2
             out = torch.empty((2 * n, H * V), device=DEV)
             ops().delta_rule(act, narrow, None, None, state, i32([0, n, 2 * n]), i32(slots), out,
-                             2, H, G, D, V, max_new=1 if n == 1 else 0, log_decay=logd, b_col=3)
+                             2, H, G, D, V, max_new=1 if n == 1 else 0, log_decay=logd, b_col=3,
+                             longest=n if tables else 0)
             got[0].append(out[:n].cpu())
             got[1].append(out[n:].cpu())
             at += size
         return [torch.cat(x) for x in got]
 
+    # (the chunks' tables of weights formed by every CTA itself, and by the kernel that forms
+    # them all before the scan)
     for cuts in ([T], [2] * 26 + [1], [21, 1, 1, 16, 14]):
-        got = run(cuts)
-        for a, b in zip(got, want):
-            torch.testing.assert_close(a, b, **tol)
+        for tables in (False, True):
+            got = run(cuts, tables)
+            for a, b in zip(got, want):
+                torch.testing.assert_close(a, b, **tol)
     # a decay that is left out, or taken per head instead of per channel, would show
     flat = [(r[0], r[1], r[2].view(T, H, D).mean(-1, keepdim=True).expand(T, H, D).reshape(T, H * D))
             for r in rows]
