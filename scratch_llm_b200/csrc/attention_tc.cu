@@ -214,6 +214,10 @@ struct AtcArgs {
     // scores, exp(sinks[h]) joins its softmax denominator once.  oob_row: a row beyond the cache
     // tensor: a copy from there brings zeros (pages the row has given back, or never held).
     int window; const float* slopes; const float* sinks; int oob_row;
+    // attn_tc_kernel<true> only.  softcap2 > 0: the scaled score s (base-2 units) becomes
+    // softcap2 * tanh(s / softcap2), before the slopes.  chunk > 0: the query at position i sees
+    // only keys from floor(i / chunk) * chunk on.
+    float softcap2; int chunk;
     // 2: a page holds keys, then values; 1: one vector per token, its key and its value
     int planes;
 };
@@ -259,7 +263,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const int tok_first = q0 / GS;
     const int last_pos = pos0 + min(n_packed - 1, q0 + TQ - 1) / GS;
     // the first key tile any query of this tile can see (tiles are counted from it below)
-    const int t_lo = (BIASED && a.window > 0) ? max(0, pos0 + tok_first - a.window + 1) / TKV : 0;
+    int t_lo = (BIASED && a.window > 0) ? max(0, pos0 + tok_first - a.window + 1) / TKV : 0;
+    if (BIASED && a.chunk > 0) t_lo = max(t_lo, (pos0 + tok_first) / a.chunk * a.chunk / TKV);
     const int n_tiles = last_pos / TKV + 1 - t_lo;
 
     if (threadIdx.x == 0) {
@@ -458,19 +463,33 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             for (int c = 0; c < 4; ++c) atc_ld32_nowait(lane_base + sp_col + c * 32, sv[c]);
             atc_ld_wait();
             bool masked = !valid || kt + TKV - 1 > qpos;
+            int lowest = -1;       // the last key position that the row does not see any more
             if (BIASED) {
                 // scores scaled and the distance's penalty taken off here, so that the maximum
                 // is the biased scores': s * scale - slope (qpos - kt) + slope * (key's index)
                 const float base = -slope2 * (float)(qpos - kt);
+                if (a.softcap2 > 0.f) {     // the cap first, then the distance's penalty
+                    const float to_cap = a.scale_log2 / a.softcap2;
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
+                    for (int c = 0; c < 4; ++c)
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        sv[c][i] = fmaf(sv[c][i], a.scale_log2, fmaf(slope2, (float)(c * 32 + i), base));
-                if (a.window > 0 && kt <= qpos - a.window) masked = true;
+                        for (int i = 0; i < 32; ++i) {
+                            float th;
+                            asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(sv[c][i] * to_cap));
+                            sv[c][i] = fmaf(th, a.softcap2, fmaf(slope2, (float)(c * 32 + i), base));
+                        }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            sv[c][i] = fmaf(sv[c][i], a.scale_log2, fmaf(slope2, (float)(c * 32 + i), base));
+                }
+                lowest = a.window > 0 ? qpos - a.window : -1;
+                if (a.chunk > 0) lowest = max(lowest, qpos / a.chunk * a.chunk - 1);
+                if (kt <= lowest) masked = true;
             }
             if (masked) {
-                const int lowest = (BIASED && a.window > 0) ? qpos - a.window : -1;   // not seen
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
 #pragma unroll
@@ -1006,14 +1025,15 @@ static int attn_tc_launch(const void* q, int64_t q_stride, int64_t n_tokens, con
                           const int* row_list, int n_list, int max_new, void* out,
                           int64_t out_stride, int H, int G, float scale, bool biased, int window,
                           const float* slopes, const float* sinks, int planes,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, float softcap = 0.f, int chunk = 0) {
     if (n_list <= 0 || max_new <= 0) return 0;
     if (!sllm_attn_tc_supports(H, G, page_size, 0) || n_list > 65535 || G > 65535 ||
         (q_stride % 8) || (out_stride % 8) || ((uintptr_t)q & 15) || ((uintptr_t)pages & 15) ||
         ((uintptr_t)out & 15))
         return (int)cudaErrorInvalidValue;
     if (n_pages * 2 * G * page_size + page_size > 0x7fffffffLL || n_tokens > 0x7fffffffLL ||
-        window < 0 || planes < 1 || planes > 2)
+        window < 0 || planes < 1 || planes > 2 || chunk < 0 || softcap < 0.f ||
+        (!biased && (chunk > 0 || softcap > 0.f)))
         return (int)cudaErrorInvalidValue;
     // the query tiles of a row are the grid's z: at most 65,535 of them
     if (((int64_t)max_new * (H / G) + TQ - 1) / TQ > 65535) return (int)cudaErrorInvalidValue;
@@ -1047,6 +1067,7 @@ static int attn_tc_launch(const void* q, int64_t q_stride, int64_t n_tokens, con
     a.out = (bf16*)out; a.out_stride = out_stride; a.H = H; a.G = G;
     a.scale_log2 = scale * 1.4426950408889634f;
     a.window = window; a.slopes = slopes; a.sinks = sinks;
+    a.softcap2 = softcap * 1.4426950408889634f; a.chunk = chunk;
     a.oob_row = (int)(n_pages * planes * G * page_size);
     a.planes = planes;
     cudaError_t e;
@@ -1104,15 +1125,17 @@ SLLM_EXPORT int sllm_attn_tc(const void* q, int64_t q_stride, int64_t n_tokens, 
 
 // The same with a sliding window (0: none), distance slopes and softmax sinks per head (float
 // [H], may be null; natural units, as the scores' scale).  Pages that a row has given back (its
-// block table holds -1 there) are never read.
+// block table holds -1 there) are never read.  softcap > 0: a tanh cap on the scaled scores;
+// chunk > 0: keys from the start of the query's chunk on (see AtcArgs).
 SLLM_EXPORT int sllm_attn_tc_biased(const void* q, int64_t q_stride, int64_t n_tokens,
                                     const void* pages, int64_t n_pages, const int* block_table,
                                     int table_stride, int page_size, const int* row_start,
                                     const int* row_pos0, const int* row_list, int n_list,
                                     int max_new, void* out, int64_t out_stride, int H, int G,
                                     float scale, int window, const float* slopes,
-                                    const float* sinks, cudaStream_t stream) {
+                                    const float* sinks, float softcap, int chunk,
+                                    cudaStream_t stream) {
     return attn_tc_launch(q, q_stride, n_tokens, pages, n_pages, block_table, table_stride,
                           page_size, row_start, row_pos0, row_list, n_list, max_new, out, out_stride,
-                          H, G, scale, true, window, slopes, sinks, 2, stream);
+                          H, G, scale, true, window, slopes, sinks, 2, stream, softcap, chunk);
 }

@@ -117,6 +117,26 @@ __device__ __forceinline__ float gate_activation_fast(float z, int act) {
     return z / (1.0f + __expf(-z));
 }
 
+// What a gated feed-forward multiplies its down matrix with, from a gate and an up value.
+// act 1, 2: act(gate) * up as above.  act 3, with p0 = a limit and p1 = a slope: the gate is
+// clamped from above and the up value on both sides, g = min(gate, p0), u = clamp(up, -p0, p0),
+// and the product is g * sigmoid(p1 * g) * (u + 1).
+__device__ __forceinline__ float gated_product(float gate, float up, int act, float p0, float p1) {
+    if (act == 3) {
+        const float g = fminf(gate, p0), u = fminf(fmaxf(up, -p0), p0);
+        return g / (1.0f + expf(-p1 * g)) * (u + 1.0f);
+    }
+    return gate_activation(gate, act) * up;
+}
+__device__ __forceinline__ float gated_product_fast(float gate, float up, int act, float p0,
+                                                    float p1) {
+    if (act == 3) {
+        const float g = fminf(gate, p0), u = fminf(fmaxf(up, -p0), p0);
+        return g / (1.0f + __expf(-p1 * g)) * (u + 1.0f);
+    }
+    return gate_activation_fast(gate, act) * up;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

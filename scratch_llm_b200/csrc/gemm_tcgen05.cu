@@ -69,7 +69,7 @@ template <bool SWIGLU>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                bf16* __restrict__ Y, int M, int N, int K, int64_t ldy, int n_half, int tiles_m,
-               int tiles_n, int act) {
+               int tiles_n, int act, float act_p0, float act_p1) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(
         ((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -197,7 +197,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                             // gate and up are rounded to bfloat16 first, as the unfused path does
                             const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gv[i])));
                             const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(uv[i])));
-                            o[i] = gate_activation_fast(g, act) * u;
+                            o[i] = gated_product_fast(g, u, act, act_p0, act_p1);
                         }
                         store_row32(Y + (int64_t)row * ldy + col, o, n_half - col, aligned);
                     }
@@ -289,7 +289,7 @@ template <bool SWIGLU>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                 bf16* __restrict__ Y, int M, int N, int K, int64_t ldy, int n_half, int tiles_m,
-                int tiles_n, int bn, int act) {
+                int tiles_n, int bn, int act, float act_p0, float act_p1) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(
         ((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -422,7 +422,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                             // gate and up are rounded to bfloat16 first, as the unfused path does
                             const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gv[i])));
                             const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(uv[i])));
-                            o[i] = gate_activation_fast(g, act) * u;
+                            o[i] = gated_product_fast(g, u, act, act_p0, act_p1);
                         }
                         const int keep = bn - c * 32;    // features of this tile left from col on
                         store_row32(Y + (int64_t)row * ldy + col, o,
@@ -525,10 +525,11 @@ SLLM_EXPORT int sllm_gemm_tc_error() {
 
 // X [M, K], W [N, K] bfloat16, 16-byte aligned with row strides that are multiples of 8;
 // Y bfloat16 [M, N] (swiglu = 0) or [M, N / 2] (W = [gate rows; up rows]; swiglu = 1: silu on
-// the gate, swiglu = 2: the tanh form of gelu).
+// the gate, swiglu = 2: the tanh form of gelu, swiglu = 3: the clamped form of common.cuh's
+// gated_product with the limit act_p0 and the slope act_p1).
 SLLM_EXPORT int sllm_gemm_tc(const void* X, const void* W, void* Y, int M, int N, int K,
-                             int64_t ldx, int64_t ldw, int64_t ldy, int swiglu,
-                             cudaStream_t stream) {
+                             int64_t ldx, int64_t ldw, int64_t ldy, int swiglu, float act_p0,
+                             float act_p1, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8) || (swiglu && (N % 2)))
         return (int)cudaErrorInvalidValue;
@@ -575,13 +576,13 @@ SLLM_EXPORT int sllm_gemm_tc(const void* X, const void* W, void* Y, int M, int N
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC2_SMEM);
             if (e2 != cudaSuccess) return (int)e2;
             e2 = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<true>, map_x, map_w, (bf16*)Y, M, N, K, ldy,
-                                    n_half, tiles_m2, tiles_n, bn, swiglu);
+                                    n_half, tiles_m2, tiles_n, bn, swiglu, act_p0, act_p1);
         } else {
             e2 = cudaFuncSetAttribute(gemm_tc2_kernel<false>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC2_SMEM);
             if (e2 != cudaSuccess) return (int)e2;
             e2 = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<false>, map_x, map_w, (bf16*)Y, M, N, K, ldy,
-                                    n_half, tiles_m2, tiles_n, 128, 0);
+                                    n_half, tiles_m2, tiles_n, 128, 0, 0.f, 0.f);
         }
         return (int)e2;
     }
@@ -594,13 +595,13 @@ SLLM_EXPORT int sllm_gemm_tc(const void* X, const void* W, void* Y, int M, int N
         if (e != cudaSuccess) return (int)e;
         gemm_tc_kernel<true><<<grid, TC_THREADS, TC_SMEM, stream>>>(map_x, map_w, (bf16*)Y, M, N, K,
                                                                   ldy, n_half, tiles_m, tiles_n,
-                                                                  swiglu);
+                                                                  swiglu, act_p0, act_p1);
     } else {
         e = cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)TC_SMEM);
         if (e != cudaSuccess) return (int)e;
         gemm_tc_kernel<false><<<grid, TC_THREADS, TC_SMEM, stream>>>(map_x, map_w, (bf16*)Y, M, N, K,
-                                                                   ldy, n_half, tiles_m, tiles_n, 0);
+                                                                   ldy, n_half, tiles_m, tiles_n, 0, 0.f, 0.f);
     }
     SLLM_LAUNCH_CHECK();
     return 0;

@@ -45,7 +45,8 @@ template <> __device__ __forceinline__ void store_out<bf16>(bf16* p, float v) {
 template <int MT, bool SWIGLU, typename TOut>
 __global__ void __launch_bounds__(GV_THREADS)
 gemv_mma_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, TOut* __restrict__ Y,
-                int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldy, int act) {
+                int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldy, int act, float act_p0,
+                float act_p1) {
     constexpr int NW = SWIGLU ? 2 : 1;
     __shared__ float red[GV_WARPS][GV_ROWS][8 * MT + 1];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -172,7 +173,7 @@ gemv_mma_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, TOut* __
             // the unfused path rounds gate and up to bfloat16 before the activation
             const float gate = __bfloat162float(__float2bfloat16_rn(v[0][i]));
             const float up = __bfloat162float(__float2bfloat16_rn(v[NW - 1][i]));
-            out = gate_activation(gate, act) * up;
+            out = gated_product(gate, up, act, act_p0, act_p1);
         }
         store_out<TOut>(Y + (int64_t)tok * ldy + n0 + r, out);
     }
@@ -182,7 +183,7 @@ static int g_gemv_pdl = 1;
 
 template <int MT, bool SWIGLU, typename TOut>
 static int launch_gemv(const void* X, const void* W, void* Y, int M, int N, int K, int64_t ldx,
-                       int64_t ldw, int64_t ldy, int act, cudaStream_t stream) {
+                       int64_t ldw, int64_t ldy, int act, float p0, float p1, cudaStream_t stream) {
     const int n_out = SWIGLU ? N / 2 : N;
     const int grid = (n_out + GV_ROWS - 1) / GV_ROWS;
     // launched so that it may start while the previous kernel of the stream drains: the kernel
@@ -198,18 +199,18 @@ static int launch_gemv(const void* X, const void* W, void* Y, int M, int N, int 
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_mma_kernel<MT, SWIGLU, TOut>, (const bf16*)X,
-                                       (const bf16*)W, (TOut*)Y, M, N, K, ldx, ldw, ldy, act);
+                                       (const bf16*)W, (TOut*)Y, M, N, K, ldx, ldw, ldy, act, p0, p1);
     if (e != cudaSuccess) return (int)e;
     return 0;
 }
 
 template <bool SWIGLU, typename TOut>
 static int pick_mt(const void* X, const void* W, void* Y, int M, int N, int K, int64_t ldx,
-                   int64_t ldw, int64_t ldy, int act, cudaStream_t stream) {
-    if (M <= 8) return launch_gemv<1, SWIGLU, TOut>(X, W, Y, M, N, K, ldx, ldw, ldy, act, stream);
-    if (M <= 16) return launch_gemv<2, SWIGLU, TOut>(X, W, Y, M, N, K, ldx, ldw, ldy, act, stream);
-    if (M <= 32) return launch_gemv<4, SWIGLU, TOut>(X, W, Y, M, N, K, ldx, ldw, ldy, act, stream);
-    return launch_gemv<8, SWIGLU, TOut>(X, W, Y, M, N, K, ldx, ldw, ldy, act, stream);
+                   int64_t ldw, int64_t ldy, int act, float p0, float p1, cudaStream_t stream) {
+    if (M <= 8) return launch_gemv<1, SWIGLU, TOut>(X, W, Y, M, N, K, ldx, ldw, ldy, act, p0, p1, stream);
+    if (M <= 16) return launch_gemv<2, SWIGLU, TOut>(X, W, Y, M, N, K, ldx, ldw, ldy, act, p0, p1, stream);
+    if (M <= 32) return launch_gemv<4, SWIGLU, TOut>(X, W, Y, M, N, K, ldx, ldw, ldy, act, p0, p1, stream);
+    return launch_gemv<8, SWIGLU, TOut>(X, W, Y, M, N, K, ldx, ldw, ldy, act, p0, p1, stream);
 }
 
 }  // namespace sllm
@@ -223,22 +224,23 @@ SLLM_EXPORT void sllm_gemv_set_pdl(int on) { g_gemv_pdl = on ? 1 : 0; }
 
 // X [M, K], W [N, K] bfloat16, rows 16-byte aligned (K, ldx, ldw multiples of 8).
 // swiglu = 0: Y [M, N].  swiglu = 1: W = [gate rows; up rows], Y [M, N / 2] = silu(gate) * up;
-// swiglu = 2: the same with the tanh form of gelu on the gate.
+// swiglu = 2: the same with the tanh form of gelu on the gate; swiglu = 3: the clamped form of
+// common.cuh's gated_product with the limit p0 and the slope p1.
 // out_dtype: 0 = float32, 1 = bfloat16.  Sizes this kernel does not take return
 // cudaErrorInvalidValue.
 SLLM_EXPORT int sllm_gemv_mma(const void* X, const void* W, void* Y, int M, int N, int K,
                               int64_t ldx, int64_t ldw, int64_t ldy, int swiglu, int out_dtype,
-                              cudaStream_t stream) {
+                              float p0, float p1, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 64 || K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8) || (swiglu && (N % 2)))
         return (int)cudaErrorInvalidValue;
     if (((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return (int)cudaErrorInvalidValue;
     if (swiglu) {
-        if (out_dtype == 1) return pick_mt<true, bf16>(X, W, Y, M, N, K, ldx, ldw, ldy, swiglu, stream);
-        if (out_dtype == 0) return pick_mt<true, float>(X, W, Y, M, N, K, ldx, ldw, ldy, swiglu, stream);
+        if (out_dtype == 1) return pick_mt<true, bf16>(X, W, Y, M, N, K, ldx, ldw, ldy, swiglu, p0, p1, stream);
+        if (out_dtype == 0) return pick_mt<true, float>(X, W, Y, M, N, K, ldx, ldw, ldy, swiglu, p0, p1, stream);
     } else {
-        if (out_dtype == 1) return pick_mt<false, bf16>(X, W, Y, M, N, K, ldx, ldw, ldy, 0, stream);
-        if (out_dtype == 0) return pick_mt<false, float>(X, W, Y, M, N, K, ldx, ldw, ldy, 0, stream);
+        if (out_dtype == 1) return pick_mt<false, bf16>(X, W, Y, M, N, K, ldx, ldw, ldy, 0, 0.f, 0.f, stream);
+        if (out_dtype == 0) return pick_mt<false, float>(X, W, Y, M, N, K, ldx, ldw, ldy, 0, 0.f, 0.f, stream);
     }
     return (int)cudaErrorInvalidValue;
 }

@@ -77,7 +77,8 @@ struct GemvTmaArgs {
     bf16* x_out;
     int64_t ld_xout;
     float* ss_out;        // [row tiles][8]
-    int act;              // with SWIGLU: 1 = silu on the gate, 2 = gelu (tanh form)
+    int act;              // with SWIGLU: 1 = silu on the gate, 2 = gelu (tanh form), 3 = clamped
+    float act_p0, act_p1; // act 3: the limit and the slope (common.cuh: gated_product)
 };
 
 // Shared memory: [barriers] | the warps' partial sums | activations | ring
@@ -283,7 +284,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemv_tma_kernel(const __grid_co
                         // the unfused path rounds gate and up to bfloat16 before the activation
                         const float gate = __bfloat162float(__float2bfloat16_rn(v[0]));
                         const float up = __bfloat162float(__float2bfloat16_rn(v[NW - 1]));
-                        y = gate_activation(gate, a.act) * up;
+                        y = gated_product(gate, up, a.act, a.act_p0, a.act_p1);
                     }
                     gt_store(reinterpret_cast<TOut*>(a.Y) + (int64_t)tok * a.ldy + feat, y);
                 }
@@ -478,7 +479,7 @@ SLLM_EXPORT int sllm_gemv_tma(const void* X, const void* W, void* Y, void* works
                               int out_dtype, int n_sm, const float* ss_in, int ss_parts,
                               int ss_dim, float ss_eps, float* resid, int64_t ld_resid,
                               const float* gain, void* x_out, int64_t ld_xout, float* ss_out,
-                              cudaStream_t stream) {
+                              float act_p0, float act_p1, cudaStream_t stream) {
     if (!sllm_gemv_tma_supports(M, N, K, swiglu, n_sm)) return (int)cudaErrorInvalidValue;
     if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15) ||
         ((uintptr_t)workspace & 15))
@@ -498,7 +499,7 @@ SLLM_EXPORT int sllm_gemv_tma(const void* X, const void* W, void* Y, void* works
     a.M = M; a.N = N; a.K = K;
     a.ldx = ldx; a.ldw = ldw; a.ldy = ldy;
     a.splits = S;
-    a.act = swiglu;
+    a.act = swiglu; a.act_p0 = act_p0; a.act_p1 = act_p1;
     a.ss_in = ss_in; a.ss_parts = ss_parts;
     a.ss_inv_dim = ss_in ? 1.0f / (float)ss_dim : 0.f; a.ss_eps = ss_eps;
     a.resid = resid; a.ld_resid = ld_resid; a.gain = gain;

@@ -318,15 +318,25 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tens
 GEMV_MAX_TOKENS = 64
 
 
-def _gate_code(swiglu: bool, activation: str) -> int:
+def _gate_code(swiglu: bool, activation) -> int:
     """What the fused gate/up kernels take: 0 = a plain product, 1 = silu(gate) * up, 2 = the
-    tanh form of gelu on the gate."""
+    tanh form of gelu on the gate, 3 = the clamped form ``("clamped", limit, slope)``."""
     if not swiglu:
         return 0
+    if isinstance(activation, tuple):
+        activation = activation[0]
     try:
-        return {"silu": 1, "gelu_tanh": 2}[activation]
+        return {"silu": 1, "gelu_tanh": 2, "clamped": 3}[activation]
     except KeyError:
         raise KernelError(f"unknown gate activation {activation!r}") from None
+
+
+def _gate_params(activation) -> tuple:
+    """The two numbers of an activation that has some: ``("clamped", limit, slope)`` is, with
+    g = min(gate, limit) and u = clamp(up, -limit, limit), g * sigmoid(slope * g) * (u + 1)."""
+    if isinstance(activation, tuple):
+        return c_float(activation[1]), c_float(activation[2])
+    return c_float(0.0), c_float(0.0)
 
 
 def gemv_mma(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = False,
@@ -349,7 +359,7 @@ def gemv_mma(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool =
     _check(_core("sllm_gemv_mma").sllm_gemv_mma(
         _ptr(x), _ptr(w), _ptr(out), c_int(m), c_int(n), c_int(k), c_int64(x.stride(0)),
         c_int64(w.stride(0)), c_int64(out.stride(0)), c_int(_gate_code(swiglu, activation)),
-        c_int(_code(out.dtype)), _stream()), "gemv_mma")
+        c_int(_code(out.dtype)), *_gate_params(activation), _stream()), "gemv_mma")
     return out
 
 
@@ -452,7 +462,8 @@ def gemv_tma(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None, swiglu:
         c_int(_gate_code(swiglu, activation)), c_int(_code(out.dtype) if out is not None else 1),
         c_int(_sm_count(x.device)), _ptr(ss_in), c_int(ss_parts), c_int(ss_dim), c_float(ss_eps),
         _ptr(resid), c_int64(resid.stride(0) if resid is not None else 0), _ptr(gain), _ptr(x_out),
-        c_int64(x_out.stride(0) if x_out is not None else 0), _ptr(ss_out), _stream()), "gemv_tma")
+        c_int64(x_out.stride(0) if x_out is not None else 0), _ptr(ss_out),
+        *_gate_params(activation), _stream()), "gemv_tma")
     if sink is not None:    # (counted beside "gemv_tma": which steps handed a norm over)
         launch_counts["gemv_tma_sink"] = launch_counts.get("gemv_tma_sink", 0) + 1
     return out
@@ -481,7 +492,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: bool = 
     _check(_core("sllm_gemm_tcgen05").sllm_gemm_tc(
         _ptr(x), _ptr(w), _ptr(out), c_int(m), c_int(n), c_int(k), c_int64(x.stride(0)),
         c_int64(w.stride(0)), c_int64(out.stride(0)), c_int(_gate_code(swiglu, activation)),
-        _stream()), "gemm_tc")
+        *_gate_params(activation), _stream()), "gemm_tc")
     return out
 
 
@@ -787,13 +798,16 @@ def attention_tc(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor
                  row_list: torch.Tensor | None, n_list: int, max_new: int, n_heads: int,
                  n_kv_heads: int, head_dim: int, scale: float, window: int | None = None,
                  slopes: torch.Tensor | None = None, sinks: torch.Tensor | None = None,
-                 biased: bool = False) -> torch.Tensor:
+                 biased: bool = False, softcap: float = 0.0,
+                 chunk: int | None = None) -> torch.Tensor:
     """Causal attention of the listed rows (prompt portions) over the paged cache on tcgen05
     tensor cores with S, P and O in tensor memory.  What the cache holds in places beyond a
     row's context never reaches a result (NaN included).  With ``biased`` (or any of ``window``,
     ``slopes``, ``sinks``, as in :func:`attention_simt`) the kernel with one query tile per CTA
-    runs, which skips key tiles behind the window and never reads pages the row gave back."""
-    biased = biased or bool(window) or slopes is not None or sinks is not None
+    runs, which skips key tiles behind the window and never reads pages the row gave back; it
+    also takes ``softcap`` and ``chunk`` (as in :func:`attention_simt`)."""
+    biased = biased or bool(window) or slopes is not None or sinks is not None \
+        or softcap > 0 or bool(chunk)
     _head_vectors(slopes, sinks, n_heads)
     _need(q, torch.bfloat16, "q", contiguous=False)
     _need(pages, torch.bfloat16, "pages")
@@ -819,7 +833,8 @@ def attention_tc(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor
         if planes != 2:
             raise KernelError("the biased tcgen05 attention takes pages of keys and values")
         _check(lib.sllm_attn_tc_biased(*common, c_int(window or 0), _ptr(slopes), _ptr(sinks),
-                                       _stream()), "attention_tc")
+                                       c_float(softcap), c_int(chunk or 0), _stream()),
+               "attention_tc")
     else:
         _check(lib.sllm_attn_tc(*common, c_int(planes), _stream()), "attention_tc")
     return out

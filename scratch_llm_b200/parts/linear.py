@@ -107,29 +107,37 @@ class Linear:
         """For a weight [gate rows; up rows]: silu(x gate^T) * (x up^T)."""
         return self.gated(x, "silu")
 
-    def gated(self, x: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+    def gated(self, x: torch.Tensor, activation="silu", out: torch.Tensor | None = None
+              ) -> torch.Tensor:
         """For a weight [gate rows; up rows]: act(x gate^T) * (x up^T) with ``activation``
-        "silu" or "gelu_tanh", fused into the product where a kernel takes the shape."""
+        "silu" or "gelu_tanh", or ``("clamped", limit, slope)``: with g = min(gate, limit) and
+        u = clamp(up, -limit, limit), g * sigmoid(slope * g) * (u + 1).  Fused into the product
+        where a kernel takes the shape.  ``out``: where to put the result (may be a column slice
+        of a wider buffer)."""
         w = self.weight
         half = self.out_features // 2
         if isinstance(x, Normed):
             if not self.takes_normed(x.x.shape[0], swiglu=True):
                 raise ValueError("this product cannot finish a deferred norm (the part that "
                                  "handed it over must ask takes_normed first)")
-            out = torch.empty((x.x.shape[0], half), dtype=x.x.dtype, device=x.x.device)
+            if out is None:
+                out = torch.empty((x.x.shape[0], half), dtype=x.x.dtype, device=x.x.device)
             return ops.gemv_tma(x.x, w, out, swiglu=True, scale=(x.shares, x.dim, x.eps),
                                 activation=activation)
-        out = torch.empty((x.shape[0], half), dtype=x.dtype, device=x.device)
+        if out is None:
+            out = torch.empty((x.shape[0], half), dtype=x.dtype, device=x.device)
         fits = (w.dtype == torch.bfloat16 and self.in_features % 8 == 0
                 and x.stride(0) % 8 == 0)
         if fits and x.shape[0] <= SMALL_BATCH:
             if self._persistent_swiglu:
                 return ops.gemv_tma(x, w, out, swiglu=True, activation=activation)
             return ops.gemv_mma(x, w, out, swiglu=True, activation=activation)
-        if fits and half % 8 == 0 and self._fused_pays(x.shape[0], half):
+        if fits and half % 8 == 0 and out.stride(0) % 8 == 0 and self._fused_pays(x.shape[0], half):
             # tcgen05 kernel with the activation in its epilogue: the [tokens, 2F] intermediate
             # is never written
             return ops.gemm_tc(x, w, out, swiglu=True, activation=activation)
-        if activation == "silu":
+        if isinstance(activation, tuple):
+            return ops.clamped_gate(self(x), out, activation[1], activation[2])
+        if activation == "silu" and out.is_contiguous():
             return ops.swiglu(self(x), out)
         return ops.gated_act(self(x), out, activation)

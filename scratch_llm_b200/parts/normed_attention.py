@@ -29,7 +29,7 @@ import torch
 
 from ..kernels import ops
 from ..weights.loader import ParamSpec
-from .attention import decode_splits
+from .attention import TC_MIN_PACKED_QUERIES, decode_splits
 from .base import BuildContext, CacheView, KVSpec, Mixer, PositionEncoding
 from .linear import Linear
 from .registry import register_mixer
@@ -92,8 +92,12 @@ class NormedAttention(Mixer):
         jobs = [ops.core_job("sllm_norm_rope_cache")]
         if self.has_gate:
             jobs.append(ops.core_job("sllm_latent_attention"))    # (its per-head gate kernel)
-        jobs.append(ops.attention_mma_library(self.head_dim) if self._tensor_cores(dtype)
-                    else ops.attention_library(self.head_dim))
+        if self._tensor_cores(dtype):
+            jobs.append(ops.attention_mma_library(self.head_dim))
+            if self.head_dim % 64 == 0:
+                jobs.append(ops.attention_tc_library(self.head_dim))
+        else:
+            jobs.append(ops.attention_library(self.head_dim))
         return jobs
 
     # ---------------------------------------------------------------------------- weights
@@ -197,13 +201,21 @@ class NormedAttention(Mixer):
         return out
 
     def _attend_tensor_cores(self, q, out, batch, cache: CacheView) -> None:
-        """Rows with several new tokens go to the wide ``mma.sync`` kernel, rows with one to the
-        split kernel (as :class:`~.attention.GQAttention` does); both take the cap, the chunks
+        """Rows with several new tokens go to the tcgen05 kernel where the longest of them fills
+        one of its query tiles, else to the wide ``mma.sync`` kernel; rows with one token to the
+        split kernel (as :class:`~.attention.GQAttention` does).  All take the cap, the chunks
         and the sink."""
         H, G, hd = self.n_heads, self.n_kv_heads, self.head_dim
         common = (q, cache.pages, cache.block_table, cache.page_size, batch.row_start,
                   batch.row_pos0, out)
-        if batch.n_multi:
+        if batch.n_multi and batch.max_new_multi * (H // G) >= TC_MIN_PACKED_QUERIES and \
+                out.stride(0) % 8 == 0 and \
+                ops.attention_tc_supports(H, G, hd, cache.page_size, self.window, biased=True):
+            # scores, probabilities and output in tensor memory
+            ops.attention_tc(*common, batch.multi_rows, batch.n_multi, batch.max_new_multi, H, G,
+                             hd, self.scale, self.window, None, self.sinks, biased=True,
+                             softcap=self.softcap, chunk=self.chunk)
+        elif batch.n_multi:
             ops.attention_mma(*common, batch.multi_rows, batch.n_multi, batch.max_new_multi, H, G,
                               hd, self.scale, self.window, split=False, sinks=self.sinks,
                               softcap=self.softcap, chunk=self.chunk)

@@ -191,6 +191,10 @@ def run_attention(kind, q, pages, table, page_size, pos0, H, G, hd, scale, n_spl
     if kind == "simt":
         o.attention_simt(qd, pages, table, page_size, row_start, row_pos0, out, 1, n, H, G, hd,
                          scale, window, None, sinks, **kw)
+    elif kind == "tc":
+        o.attention_tc(qd, pages, table, page_size, row_start, row_pos0, out, i32([0]), 1, n, H, G,
+                       hd, scale, window, None, sinks, biased=True, **kw)
+        assert o.attention_tc_error(hd) == 0
     else:
         scratch = None
         if n_splits > 1:
@@ -209,6 +213,9 @@ CASES = [  # kind, dtype, head size, new tokens, splits
     ("wide", torch.bfloat16, 128, 2, 1),
     ("split", torch.bfloat16, 64, 1, 1), ("split", torch.bfloat16, 64, 1, 3),
     ("split", torch.bfloat16, 32, 1, 2), ("split", torch.bfloat16, 128, 1, 2),
+    # tcgen05: query tiles of 64 tokens x 2 heads, a ragged second one
+    ("tc", torch.bfloat16, 64, 64, 1), ("tc", torch.bfloat16, 64, 100, 1),
+    ("tc", torch.bfloat16, 128, 130, 1),
 ]
 
 
