@@ -211,25 +211,32 @@ lowrank_decay_kernel(const float* __restrict__ pre, int64_t ldp, const float* __
 //     mode 0:  out = z
 //     mode 1:  out = -exp(rate_log[c / per_rate]) * softplus(z)    (the logarithm of a decay
 //              exp(-exp(A) softplus(z)) with one A per `per_rate` channels)
-// The sum runs over r in ascending order for every token, whatever the batch.  out: [N, C] of
-// TO.  grid (ceil(C / 256), ceil(N / LOWRANK_TOKENS)); shared: LOWRANK_TOKENS * R floats.
-template <typename TO>
+// The sum runs over r in ascending order for every token, whatever the batch.  out: [N, C],
+// float32 or bfloat16.  One launch serves up to two such products of the same `pre` (a mixer's
+// decays and its gate): the first `blocks0` CTAs along x take the first job, the rest the second.
+// grid (blocks of both jobs, ceil(N / LOWRANK_TOKENS)); shared: LOWRANK_TOKENS * max R floats.
+struct ExpandJob {
+    int col0; const float* w2t; const float* bias; const float* rate_log; int per_rate; int mode;
+    void* out; int out_bf16; int C; int R;
+};
+
 __global__ void __launch_bounds__(256)
-lowrank_expand_kernel(const float* __restrict__ pre, int64_t ldp, int col0,
-                      const float* __restrict__ w2t, const float* __restrict__ bias,
-                      const float* __restrict__ rate_log, int per_rate, int mode,
-                      TO* __restrict__ out, int N, int C, int R) {
+lowrank_expand_kernel(const float* __restrict__ pre, int64_t ldp, const ExpandJob j0,
+                      const ExpandJob j1, int blocks0, int N) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ float th[];   // [LOWRANK_TOKENS][R]
+    const bool second = (int)blockIdx.x >= blocks0;
+    const ExpandJob& j = second ? j1 : j0;
+    const int R = j.R, C = j.C;
     const int n0 = blockIdx.y * LOWRANK_TOKENS;
     const int nt = min(LOWRANK_TOKENS, N - n0);
     for (int i = threadIdx.x; i < LOWRANK_TOKENS * R; i += blockDim.x) {
         const int t = i / R, r = i - t * R;
-        th[t * R + r] = t < nt ? pre[(int64_t)(n0 + t) * ldp + col0 + r] : 0.f;
+        th[t * R + r] = t < nt ? pre[(int64_t)(n0 + t) * ldp + j.col0 + r] : 0.f;
     }
     __syncthreads();
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int c = ((int)blockIdx.x - (second ? blocks0 : 0)) * blockDim.x + threadIdx.x;
     if (c >= C) return;
     float acc[LOWRANK_TOKENS];
 #pragma unroll
@@ -238,25 +245,27 @@ lowrank_expand_kernel(const float* __restrict__ pre, int64_t ldp, int col0,
     for (; r + 16 <= R; r += 16) {
         float w[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) w[j] = w2t[(int64_t)(r + j) * C + c];
+        for (int k = 0; k < 16; ++k) w[k] = j.w2t[(int64_t)(r + k) * C + c];
 #pragma unroll
-        for (int j = 0; j < 16; ++j)
+        for (int k = 0; k < 16; ++k)
 #pragma unroll
-            for (int t = 0; t < LOWRANK_TOKENS; ++t) acc[t] = fmaf(w[j], th[t * R + r + j], acc[t]);
+            for (int t = 0; t < LOWRANK_TOKENS; ++t) acc[t] = fmaf(w[k], th[t * R + r + k], acc[t]);
     }
     for (; r < R; ++r) {
-        const float w = w2t[(int64_t)r * C + c];
+        const float w = j.w2t[(int64_t)r * C + c];
 #pragma unroll
         for (int t = 0; t < LOWRANK_TOKENS; ++t) acc[t] = fmaf(w, th[t * R + r], acc[t]);
     }
-    const float b0 = bias ? bias[c] : 0.f;
-    const float rate = mode == 1 ? expf(rate_log[c / per_rate]) : 0.f;
+    const float b0 = j.bias ? j.bias[c] : 0.f;
+    const float rate = j.mode == 1 ? expf(j.rate_log[c / j.per_rate]) : 0.f;
 #pragma unroll
     for (int t = 0; t < LOWRANK_TOKENS; ++t) {
         if (t < nt) {
             float z = acc[t] + b0;
-            if (mode == 1) z = -rate * (z > 20.f ? z : log1pf(expf(z)));
-            out[(int64_t)(n0 + t) * C + c] = from_float<TO>(z);
+            if (j.mode == 1) z = -rate * (z > 20.f ? z : log1pf(expf(z)));
+            const int64_t at = (int64_t)(n0 + t) * C + c;
+            if (j.out_bf16) reinterpret_cast<__nv_bfloat16*>(j.out)[at] = __float2bfloat16_rn(z);
+            else reinterpret_cast<float*>(j.out)[at] = z;
         }
     }
 }
@@ -353,26 +362,38 @@ SLLM_EXPORT int sllm_lowrank_decay(const float* pre, int64_t ldp, const float* w
     return 0;
 }
 
-// out_dtype: 0 = float32, 1 = bfloat16.  mode 1 needs rate_log (float [C / per_rate]).
-SLLM_EXPORT int sllm_lowrank_expand(const float* pre, int64_t ldp, int col0, const float* w2t,
-                                    const float* bias, const float* rate_log, int per_rate,
-                                    int mode, void* out, int out_dtype, int n_tokens, int C, int R,
+// Up to two products of one `pre` in a launch (n_jobs 1 or 2); per job: col0, w2t [R, C], bias
+// (may be null), rate_log with per_rate (mode 1), mode, out [N, C], out_dtype (0 = float32,
+// 1 = bfloat16), C, R.
+SLLM_EXPORT int sllm_lowrank_expand(const float* pre, int64_t ldp, int n_jobs, const int* col0,
+                                    const float* const* w2t, const float* const* bias,
+                                    const float* const* rate_log, const int* per_rate,
+                                    const int* mode, void* const* out, const int* out_dtype,
+                                    const int* C, const int* R, int n_tokens,
                                     cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (C <= 0 || R <= 0 || R > 1024 || col0 < 0 || ldp < col0 + R || mode < 0 || mode > 1 ||
-        (mode == 1 && (!rate_log || per_rate <= 0 || C % per_rate)))
-        return (int)cudaErrorInvalidValue;
-    dim3 grid((C + 255) / 256, (n_tokens + LOWRANK_TOKENS - 1) / LOWRANK_TOKENS);
+    if (n_jobs < 1 || n_jobs > 2) return (int)cudaErrorInvalidValue;
+    ExpandJob j[2] = {};
+    int max_r = 0, max_c = 0;
+    for (int i = 0; i < n_jobs; ++i) {
+        if (C[i] <= 0 || R[i] <= 0 || R[i] > 1024 || col0[i] < 0 || ldp < col0[i] + R[i] ||
+            mode[i] < 0 || mode[i] > 1 || out_dtype[i] < 0 || out_dtype[i] > 1 ||
+            (mode[i] == 1 && (!rate_log[i] || per_rate[i] <= 0 || C[i] % per_rate[i])))
+            return (int)cudaErrorInvalidValue;
+        j[i].col0 = col0[i]; j[i].w2t = w2t[i]; j[i].bias = bias[i]; j[i].rate_log = rate_log[i];
+        j[i].per_rate = per_rate[i]; j[i].mode = mode[i]; j[i].out = out[i];
+        j[i].out_bf16 = out_dtype[i]; j[i].C = C[i]; j[i].R = R[i];
+        max_r = R[i] > max_r ? R[i] : max_r;
+        max_c = C[i] > max_c ? C[i] : max_c;
+    }
+    // steps of few tokens: narrow CTAs, so that the channels spread over more SMs
+    const int threads = n_tokens <= 2 * LOWRANK_TOKENS && max_c >= 1024 ? 64 : 256;
+    const int blocks0 = (j[0].C + threads - 1) / threads;
+    const int blocks1 = n_jobs > 1 ? (j[1].C + threads - 1) / threads : 0;
+    dim3 grid(blocks0 + blocks1, (n_tokens + LOWRANK_TOKENS - 1) / LOWRANK_TOKENS);
     if (grid.y > 65535) return (int)cudaErrorInvalidValue;
-    const size_t smem = LOWRANK_TOKENS * R * sizeof(float);
-    if (out_dtype == 0)
-        lowrank_expand_kernel<float><<<grid, 256, smem, stream>>>(
-            pre, ldp, col0, w2t, bias, rate_log, per_rate, mode, (float*)out, n_tokens, C, R);
-    else if (out_dtype == 1)
-        lowrank_expand_kernel<__nv_bfloat16><<<grid, 256, smem, stream>>>(
-            pre, ldp, col0, w2t, bias, rate_log, per_rate, mode, (__nv_bfloat16*)out, n_tokens, C, R);
-    else
-        return (int)cudaErrorInvalidValue;
+    lowrank_expand_kernel<<<grid, threads, LOWRANK_TOKENS * max_r * sizeof(float), stream>>>(
+        pre, ldp, j[0], j[1], blocks0, n_tokens);
     SLLM_LAUNCH_CHECK();
     return 0;
 }

@@ -1618,33 +1618,44 @@ def _delta_rule_channels(act, ab, state, row_start, row_slot, out, n_rows, n_hea
 
 def lowrank_expand(pre: torch.Tensor, col0: int, w2t: torch.Tensor, out: torch.Tensor,
                    bias: torch.Tensor | None = None, rate_log: torch.Tensor | None = None,
-                   per_rate: int = 0) -> torch.Tensor:
+                   per_rate: int = 0, also: tuple | None = None) -> torch.Tensor:
     """The second product of a low-rank pair in 32-bit (csrc/recurrent_ops.cu): ``pre`` float32
     [N, *] holds the hidden values in columns ``[col0, col0 + R)``, ``w2t`` float32 [R, C];
     ``out`` [N, C] (float32 or bfloat16) gets ``bias + hidden w2t``, or, with ``rate_log``
     (float32 [C / per_rate]), ``-exp(rate_log[c // per_rate]) * softplus(bias + hidden w2t)``:
-    the logarithm of a decay per channel."""
+    the logarithm of a decay per channel.  ``also = (col0, w2t, out)``: a second plain product of
+    the same ``pre`` in the same launch."""
     _need(pre, torch.float32, "pre", contiguous=False)
-    _need(w2t, torch.float32, "w2t")
-    _need(out, None, "out")
-    r, c = w2t.shape
     n = pre.shape[0]
-    if pre.stride(1) != 1 or col0 < 0 or pre.shape[1] < col0 + r or out.shape != (n, c):
+    if pre.stride(1) != 1:
         raise KernelError("lowrank_expand shapes")
-    if bias is not None:
-        _need(bias, torch.float32, "bias")
-        if bias.numel() != c:
-            raise KernelError("lowrank_expand: one bias per output channel")
-    mode = 0
-    if rate_log is not None:
-        _need(rate_log, torch.float32, "rate_log")
-        if per_rate < 1 or c % per_rate or rate_log.numel() != c // per_rate:
-            raise KernelError("lowrank_expand: one rate per `per_rate` channels")
-        mode = 1
+    jobs = [(col0, w2t, out, bias, rate_log, per_rate)]
+    if also is not None:
+        jobs.append((also[0], also[1], also[2], None, None, 0))
+    for c0, w, o, b, rl, per in jobs:
+        _need(w, torch.float32, "w2t")
+        _need(o, None, "out")
+        r, c = w.shape
+        if c0 < 0 or pre.shape[1] < c0 + r or o.shape != (n, c):
+            raise KernelError("lowrank_expand shapes")
+        if b is not None:
+            _need(b, torch.float32, "bias")
+            if b.numel() != c:
+                raise KernelError("lowrank_expand: one bias per output channel")
+        if rl is not None:
+            _need(rl, torch.float32, "rate_log")
+            if per < 1 or c % per or rl.numel() != c // per:
+                raise KernelError("lowrank_expand: one rate per `per_rate` channels")
+    k = len(jobs)
+    ints = lambda vals: (c_int * k)(*vals)  # noqa: E731
+    ptrs = lambda ts: (c_void_p * k)(*[None if t is None else t.data_ptr() for t in ts])  # noqa: E731
     _check(_core("sllm_recurrent_ops").sllm_lowrank_expand(
-        _ptr(pre), c_int64(pre.stride(0)), c_int(col0), _ptr(w2t), _ptr(bias), _ptr(rate_log),
-        c_int(per_rate), c_int(mode), _ptr(out), c_int(_code(out.dtype)), c_int(n), c_int(c),
-        c_int(r), _stream()), "lowrank_expand")
+        _ptr(pre), c_int64(pre.stride(0)), c_int(k), ints([j[0] for j in jobs]),
+        ptrs([j[1] for j in jobs]), ptrs([j[3] for j in jobs]), ptrs([j[4] for j in jobs]),
+        ints([j[5] for j in jobs]), ints([int(j[4] is not None) for j in jobs]),
+        ptrs([j[2] for j in jobs]), ints([_code(j[2].dtype) for j in jobs]),
+        ints([j[1].shape[1] for j in jobs]), ints([j[1].shape[0] for j in jobs]), c_int(n),
+        _stream()), "lowrank_expand")
     return out
 
 

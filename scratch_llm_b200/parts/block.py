@@ -237,7 +237,9 @@ class SharedNormBlock(Block):
             self._join_outputs()
         if self._joint is not False:
             w = self._joint.weight
-            cat = (torch.zeros if self._zero_fill else torch.empty)(
+            # (zeros where segments are padded up to 16 bytes, and in padded steps, whose padding
+            # tokens some branches leave unwritten)
+            cat = (torch.zeros if self._zero_fill or batch.padded else torch.empty)(
                 (h.shape[0], w.shape[1]), dtype=w.dtype, device=w.device)
             outs = [cat[:, a:a + n] for a, n in self._widths]
             self.mixer.activations_into(h, batch, cache, write, self.position,

@@ -169,16 +169,21 @@ class GatedDeltaRule(Mixer):
             b_end = 2 * H
         else:
             # the logarithms of the channels' decays, 32-bit from the first product's output on
+            # (a low-rank gate's second product rides along in the same launch)
             log_decay = torch.empty((n, H * D), dtype=torch.float32, device=proj.device)
+            if self.gate_rank is not None:
+                gate = torch.empty((n, H * V), dtype=proj.dtype, device=proj.device)
+                also = (self.decay_rank + H, self.g2t, gate)
             ops.lowrank_expand(ab, 0, self.a2t, log_decay, bias=self.dt_bias,
-                               rate_log=self.a_log, per_rate=D)
+                               rate_log=self.a_log, per_rate=D,
+                               also=also if self.gate_rank is not None else None)
             ops.delta_rule(act, ab, None, None, S, batch.row_start, batch.row_slot, o,
                            batch.n_rows, H, G, D, V, max_new=max_new, log_decay=log_decay,
                            b_col=self.decay_rank, longest=batch.max_new)
             b_end = self.decay_rank + H
         if self.gate_rank is None:
             gate = proj[:, C:C + H * V]
-        else:
+        elif self.decay_rank is None:
             gate = torch.empty((n, H * V), dtype=proj.dtype, device=proj.device)
             ops.lowrank_expand(ab, b_end, self.g2t, gate)
         if out is None:

@@ -167,7 +167,8 @@ class NormedAttention(Mixer):
     def heads_out(self, x, batch, cache: CacheView, write: bool, position: PositionEncoding,
                   out: torch.Tensor | None = None) -> torch.Tensor:
         """The concatenated heads' outputs [N, H * head_dim], gated: what
-        the output matrix multiplies.  ``out``: where to put them (may be a column slice)."""
+        the output matrix multiplies.  ``out``: where to put them (may be a column slice; in a
+        padded step it must hold zeros, since padding tokens get no attention output)."""
         H, G, hd = self.n_heads, self.n_kv_heads, self.head_dim
         if self.borrow_kv == write:
             raise ValueError("a mixer with keys of its own writes its cache entry; one that "
@@ -186,8 +187,6 @@ class NormedAttention(Mixer):
             # (padding tokens get no attention output: zeros, so that what follows stays finite)
             out = (torch.zeros if batch.padded else torch.empty)(
                 (proj.shape[0], H * hd), dtype=proj.dtype, device=proj.device)
-        elif batch.padded:
-            out.zero_()
         if self._tensor_cores(proj.dtype):
             self._attend_tensor_cores(q, out, batch, cache)
         else:

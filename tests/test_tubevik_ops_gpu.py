@@ -89,6 +89,16 @@ def test_clamped_gate_and_low_rank_products():
     half = torch.empty((n, heads * per), dtype=torch.bfloat16, device=DEV)
     ops().lowrank_expand(pre.to(DEV), 4, w2.t().contiguous().to(DEV), half)
     torch.testing.assert_close(half.float().cpu(), z.float(), rtol=1e-2, atol=1e-2)
+    # two products of the same hidden values' buffer in one launch, of other ranks and widths
+    w3 = rnd(g, (9, 3))
+    out.zero_()
+    second = torch.empty((n, 9), dtype=torch.bfloat16, device=DEV)
+    ops().lowrank_expand(pre.to(DEV), 4, w2.t().contiguous().to(DEV), out, bias=bias.to(DEV),
+                         rate_log=rate.to(DEV), per_rate=per,
+                         also=(1, w3.t().contiguous().to(DEV), second))
+    torch.testing.assert_close(out.cpu(), want.float(), rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(second.float().cpu(), (pre[:, 1:4].double() @ w3.double().T).float(),
+                               rtol=1e-2, atol=1e-2)
 
 
 # --------------------------------------------------- norms and rotation in front of attention
