@@ -251,8 +251,22 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(const DeltaArgs a) 
     Piece raw[QK_ITEMS];
     T raw_v = from_float<T>(0.f);
     float raw_a = 0.f, raw_b = 0.f;
+    // a decay per channel: the chunk's log decays and this thread's entry of its table of weights
+    // travel with the same request
+    constexpr int L_ITEMS = CHANNEL ? (TC * D + THREADS - 1) / THREADS : 1;
+    float raw_l[L_ITEMS], raw_w = 0.f;
     auto fetch = [&](int c0) {     // requests the chunk at c0 (tokens beyond the row: nothing)
         const int nt = min(TC, n_new - c0);
+        if (CHANNEL) {
+            const float* lg = a.log_decay + (int64_t)(t0 + c0) * a.ld_decay + (int64_t)head * D;
+#pragma unroll
+            for (int i = 0; i < L_ITEMS; ++i) {
+                const int idx = tid + i * THREADS, t = idx / D, e = idx - t * D;
+                raw_l[i] = (idx < TC * D && t < nt) ? lg[(int64_t)t * a.ld_decay + e] : 0.f;
+            }
+            if (a.tables != nullptr)
+                raw_w = a.tables[(((int64_t)(t0 + c0) / TC + r) * a.H + head) * 2 * TC * TC + tid];
+        }
 #pragma unroll
         for (int i = 0; i < QK_ITEMS; ++i) {
             const int item = tid + i * THREADS;
@@ -312,12 +326,14 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(const DeltaArgs a) 
         const int nt = min(TC, n_new - c0);
         __syncthreads();   // the previous chunk's staging is no longer read
         commit(nt);
+        float table_entry = 0.f;
         if (CHANNEL) {     // the chunk's log decays per channel (zeros beyond its tokens)
-            const float* lg = a.log_decay + (int64_t)(t0 + c0) * a.ld_decay + (int64_t)head * D;
-            for (int idx = tid; idx < TC * D; idx += THREADS) {
-                const int t = idx / D, e = idx - t * D;
-                lam[t][e] = t < nt ? lg[(int64_t)t * a.ld_decay + e] : 0.f;
+#pragma unroll
+            for (int i = 0; i < L_ITEMS; ++i) {
+                const int idx = tid + i * THREADS, t = idx / D, e = idx - t * D;
+                if (idx < TC * D) lam[t][e] = raw_l[i];
             }
+            table_entry = raw_w;
         }
         if (c0 + TC < n_new) fetch(c0 + TC);   // in flight while this chunk is worked on
         __syncthreads();
@@ -368,7 +384,7 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(const DeltaArgs a) 
             float dot = 0.f;
             const bool used = t < nt && s < nt && (with_q ? s <= t : s < t);
             if (CHANNEL && a.tables != nullptr) {
-                dot = a.tables[((((int64_t)(t0 + c0) / TC + r) * a.H + head) * 2 * TC + row) * TC + s];
+                dot = table_entry;       // (entry [row][s] = [tid / TC][tid % TC], as requested)
             } else if (used && CHANNEL) {
                 const float* x = with_q ? &qs[t][0] : &ks[t][0];
                 for (int e = 0; e < D; ++e)
