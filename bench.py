@@ -172,18 +172,18 @@ def tubevik_config(name: str):
 
     z = COMPARE_SIZES[name]
     mlp = {"kind": "dense", "ff": z["ff"], "limit": 7.0}
-    rot = {"base": 1000000.0, "dims": z["dim"],
-           "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}
+    rot = {"base": 2000000.0, "dims": z["dim"],
+           "scaling": {"factor": 4.0, "original": 2048, "fast": 16.0, "slow": 2.0}}
     attention = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
-                 "scale": z["dim"] ** -0.5, "softcap": 30.0, "mask": {"size": z["window"]},
+                 "scale": z["dim"] ** -0.5, "softcap": 50.0, "mask": {"size": z["window"]},
                  "rot": rot}
     left = {"heads": z["heads"] // 2, "kv_heads": z["kv_heads"] // 2, "dim": z["dim"],
             "vdim": z["dim"], "scale": 1.0, "mask": {"size": z["window"]},
-            "rot": {"base": 500000.0, "dims": z["dim"] // 2}}
-    both = {"left": left, "right": dict(z["delta"]), "left_scale": 0.8, "right_scale": 1.1}
+            "rot": {"base": 100000.0, "dims": z["dim"] // 2}}
+    both = {"left": left, "right": dict(z["delta"]), "left_scale": 0.7, "right_scale": 1.3}
     return config_from_dict({
         "architecture": "Tubevik", "vocab": z["vocab"], "width": z["width"],
-        "norm": {"eps": 1e-5}, "residual_mult": 0.5, "logit_softcap": 30.0, "max_position": 8192,
+        "norm": {"eps": 1e-5}, "residual_mult": 0.6, "logit_softcap": 40.0, "max_position": 8192,
         "layers": [{"type": "attention", "mixer": attention, "mlp": mlp},
                    {"type": "parallel", "mixer": both, "mlp": mlp},
                    {"type": "attention", "mixer": dict(attention, kv_from=0), "mlp": mlp},

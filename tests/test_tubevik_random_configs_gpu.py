@@ -30,7 +30,7 @@ def draw_attention(rng, kv_from=None, like=None):
         sc = rot.get("scaling")
         return U.attention(m["heads"], m["kv_heads"], m["dim"], m["vdim"],
                            rng.choice([1, 3, 17, 40, 200]), rot_dims=rot["dims"], base=rot["base"],
-                           scale=rng.choice([0.1, 0.3]), softcap=rng.choice([None, 5.0, 30.0]),
+                           scale=rng.choice([0.1, 0.3]), softcap=rng.choice([None, 5.0, 25.0]),
                            scaling=None if sc is None else tuple(sc[k] for k in
                                                                   ("factor", "original", "fast", "slow")),
                            kv_from=kv_from, mlp=draw_mlp(rng))
@@ -44,20 +44,20 @@ def draw_attention(rng, kv_from=None, like=None):
         scaling = (rng.choice([1.5, 2.0, 8.0]), rng.choice([16, 64, 512]),
                    rng.choice([4.0, 32.0]), rng.choice([0.5, 1.0]))
     return U.attention(kv * rng.choice([1, 2, 4]), kv, dim, vdim, rng.choice([1, 5, 24, 60, 300]),
-                       rot_dims=rot_dims, base=rng.choice([30.0, 10000.0, 1e6]),
+                       rot_dims=rot_dims, base=rng.choice([30.0, 10000.0, 2e6]),
                        scale=rng.choice([0.1, 0.3, dim ** -0.5]),
-                       softcap=rng.choice([None, 3.0, 30.0]), scaling=scaling, mlp=draw_mlp(rng))
+                       softcap=rng.choice([None, 3.0, 25.0]), scaling=scaling, mlp=draw_mlp(rng))
 
 
 def draw_parallel(rng):
     dim, vdim = rng.choice([(8, 16), (12, 10), (32, 32), (64, 64), (64, 24)])
     kv = rng.choice([1, 2])
     left = (kv * rng.choice([1, 2, 3]), kv, dim, vdim, rng.choice([1, 4, 19, 64, 250]),
-            2 * rng.randint(1, dim // 2), rng.choice([50.0, 5e5]), rng.choice([0.125, 0.4]))
+            2 * rng.randint(1, dim // 2), rng.choice([50.0, 3e5]), rng.choice([0.15, 0.4]))
     rkv = rng.choice([1, 2, 3])
     right = (rkv * rng.choice([1, 2]), rkv, rng.choice([8, 16, 33, 64]),
              rng.choice([4, 16, 24, 64]), rng.choice([1, 2, 4]))
-    return U.parallel(left, right, rng.choice([1.0, 0.8, -0.5]), rng.choice([1.0, 1.1, 0.3]),
+    return U.parallel(left, right, rng.choice([1.0, 0.75, -0.5]), rng.choice([1.0, 1.25, 0.3]),
                       mlp=draw_mlp(rng))
 
 
@@ -77,7 +77,7 @@ def draw(seed):
             layers.append(draw_attention(rng, kv_from=j, like=layers[j]))
     cfg = U.config(rng.choice([50, 128, 301]), rng.choice([32, 40, 64, 96, 128, 256]), layers,
                    eps=rng.choice([1e-5, 1e-6, 3e-4]), residual_mult=rng.choice([1.0, 0.5, 0.3]),
-                   logit_softcap=rng.choice([0.0, 10.0, 30.0]))
+                   logit_softcap=rng.choice([0.0, 10.0, 20.0]))
     lengths = [rng.randint(1, 140) for _ in range(5)] + [rng.choice([1, 2])]
     return cfg, lengths, rng.choice([8, 16, 32, 64])
 

@@ -68,13 +68,13 @@ CONFIGS = {
     # head sizes 64 and 128: the shapes of the tensor-core attention kernels; a key size of 128
     # in the recurrence
     "R": config(300, 128, [
-        attention(4, 2, 64, 64, 100, base=1e6, softcap=30.0, scaling=(2.0, 64, 32.0, 1.0),
-                  mlp=dense(192, 1.0)),
-        parallel((4, 1, 128, 128, 64, 64, 5e5, 0.09), (2, 1, 128, 64, 4), 0.8, 1.1,
-                 mlp=dense(160, 1.0)),
-        attention(4, 2, 64, 64, 130, base=1e6, softcap=30.0, scaling=(2.0, 64, 32.0, 1.0),
-                  kv_from=0, mlp=dense(96, 1.0)),
-    ], eps=1e-5, residual_mult=0.5, logit_softcap=30.0),
+        attention(4, 2, 64, 64, 100, base=2e5, softcap=20.0, scaling=(4.0, 128, 16.0, 2.0),
+                  mlp=dense(192, 1.5)),
+        parallel((4, 1, 128, 128, 64, 64, 1e5, 0.09), (2, 1, 128, 64, 4), 0.9, 1.2,
+                 mlp=dense(160, 2.0)),
+        attention(4, 2, 64, 64, 130, base=2e5, softcap=20.0, scaling=(4.0, 128, 16.0, 2.0),
+                  kv_from=0, mlp=dense(96, 1.5)),
+    ], eps=1e-5, residual_mult=0.4, logit_softcap=25.0),
 }
 
 
