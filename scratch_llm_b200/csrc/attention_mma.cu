@@ -90,6 +90,18 @@ __device__ __forceinline__ float quad_sum(float v) {
 __device__ __forceinline__ float sigmoid_of(bf16 g) {
     return 1.0f / (1.0f + __expf(-__bfloat162float(g)));
 }
+// sigmoid of the gate for elements d and d + 1 of head `head` of token `tok` (d even); with
+// per_head the gate has one number per token and head (column `head`).
+__device__ __forceinline__ float2 gate_pair(const bf16* gate, int64_t stride, int per_head,
+                                            int64_t tok, int head, int d) {
+    if (per_head) {
+        const float s1 = sigmoid_of(gate[tok * stride + head]);
+        return make_float2(s1, s1);
+    }
+    const __nv_bfloat162 g2 =
+        *reinterpret_cast<const __nv_bfloat162*>(gate + tok * stride + (int64_t)head * HD + d);
+    return make_float2(sigmoid_of(__low2bfloat16(g2)), sigmoid_of(__high2bfloat16(g2)));
+}
 
 template <bool SPLIT> struct Mode {
     static constexpr int BQ = SPLIT ? 16 : 64;
@@ -131,6 +143,8 @@ struct AttnArgs {
     // every output element is multiplied by sigmoid(gate) before it is stored (an output gate on
     // the heads; with several splits where they are merged).
     const bf16* gate = nullptr; int64_t gate_stride = 0;
+    // gate_per_head: the gate has ONE number per token and head instead, head h at column h
+    int gate_per_head = 0;
     // attn_decode_cs_kernel only.  cos_t != nullptr: q, k and v are taken from the step's fused
     // projection as they are (q points at its first column): the kernel rotates q and the row's
     // new key itself and, if write_kv, stores the new key and value.
@@ -407,15 +421,14 @@ __global__ void __launch_bounds__(THREADS, SPLIT ? 3 : 2) attn_mma_kernel(const 
             const float inv = total > 0.f ? keep / total : 0.f;
             bf16* dst = a.out + (int64_t)(t0 + tok) * a.out_stride + (int64_t)(g * GS + j) * HD +
                         (lane & 3) * 2;
-            const bf16* gt = a.gate ? a.gate + (int64_t)(t0 + tok) * a.gate_stride +
-                                          (int64_t)(g * GS + j) * HD + (lane & 3) * 2 : nullptr;
 #pragma unroll
             for (int dn = 0; dn < DTILES; ++dn) {
                 float x0 = o[dn][2 * h] * inv, x1 = o[dn][2 * h + 1] * inv;
-                if (gt) {   // (two neighbours of the gate's row: one 4-byte load)
-                    const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(gt + dn * 8);
-                    x0 *= sigmoid_of(__low2bfloat16(g2));
-                    x1 *= sigmoid_of(__high2bfloat16(g2));
+                if (a.gate) {   // (two neighbours of the gate's row: one 4-byte load)
+                    const float2 gg = gate_pair(a.gate, a.gate_stride, a.gate_per_head, t0 + tok,
+                                                g * GS + j, (lane & 3) * 2 + dn * 8);
+                    x0 *= gg.x;
+                    x1 *= gg.y;
                 }
                 *reinterpret_cast<__nv_bfloat162*>(dst + dn * 8) = __floats2bfloat162_rn(x0, x1);
             }
@@ -470,7 +483,8 @@ __global__ void __launch_bounds__(THREADS, SPLIT ? 3 : 2) attn_mma_kernel(const 
         if (n_splits == 1) {
             const int64_t col = (int64_t)(g * GS + j) * HD + d;
             const float gated = a.gate
-                ? val * sigmoid_of(a.gate[(int64_t)(t0 + tok) * a.gate_stride + col]) : val;
+                ? val * sigmoid_of(a.gate[(int64_t)(t0 + tok) * a.gate_stride +
+                                          (a.gate_per_head ? (int64_t)(g * GS + j) : col)]) : val;
             a.out[(int64_t)(t0 + tok) * a.out_stride + col] = __float2bfloat16_rn(gated);
         } else if (t0 + tok < a.part_tokens) {
             a.part_o[(qh * n_splits + split) * HD + d] = val;
@@ -857,15 +871,14 @@ __global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnAr
         const int col0 = warp * CS_OC + (lane & 3) * 2;
         if (n_splits == 1) {
             bf16* dst = a.out + (int64_t)(t0 + tok) * a.out_stride + (int64_t)(g * GS + j) * HD + col0;
-            const bf16* gt = a.gate ? a.gate + (int64_t)(t0 + tok) * a.gate_stride +
-                                          (int64_t)(g * GS + j) * HD + col0 : nullptr;
 #pragma unroll
             for (int dn = 0; dn < CS_OT; ++dn) {
                 float x0 = o[dn][2 * h] * inv, x1 = o[dn][2 * h + 1] * inv;
-                if (gt) {   // (two neighbours of the gate's row: one 4-byte load)
-                    const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(gt + dn * 8);
-                    x0 *= sigmoid_of(__low2bfloat16(g2));
-                    x1 *= sigmoid_of(__high2bfloat16(g2));
+                if (a.gate) {   // (two neighbours of the gate's row: one 4-byte load)
+                    const float2 gg = gate_pair(a.gate, a.gate_stride, a.gate_per_head, t0 + tok,
+                                                g * GS + j, col0 + dn * 8);
+                    x0 *= gg.x;
+                    x1 *= gg.y;
                 }
                 *reinterpret_cast<__nv_bfloat162*>(dst + dn * 8) = __floats2bfloat162_rn(x0, x1);
             }
@@ -933,10 +946,11 @@ __global__ void __launch_bounds__(THREADS, 3) attn_decode_cs_kernel(const AttnAr
             float4 r = make_float4(some ? num.x / den : 0.f, some ? num.y / den : 0.f,
                                    some ? num.z / den : 0.f, some ? num.w / den : 0.f);
             if (a.gate) {
-                const bf16* gt = a.gate + (int64_t)(t0 + tok) * a.gate_stride +
-                                 (int64_t)(g * GS + j) * HD + d;
-                r.x *= sigmoid_of(gt[0]); r.y *= sigmoid_of(gt[1]);
-                r.z *= sigmoid_of(gt[2]); r.w *= sigmoid_of(gt[3]);
+                const float2 ga = gate_pair(a.gate, a.gate_stride, a.gate_per_head, t0 + tok,
+                                            g * GS + j, d);
+                const float2 gb = gate_pair(a.gate, a.gate_stride, a.gate_per_head, t0 + tok,
+                                            g * GS + j, d + 2);
+                r.x *= ga.x; r.y *= ga.y; r.z *= gb.x; r.w *= gb.y;
             }
             *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(r.x, r.y);
             *reinterpret_cast<__nv_bfloat162*>(dst + 2) = __floats2bfloat162_rn(r.z, r.w);
@@ -956,7 +970,8 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) attn_merge_kernel(
         const float* __restrict__ part_o, const float* __restrict__ part_lse, int n_splits,
         const int* __restrict__ row_start, const int* __restrict__ row_list,
         bf16* __restrict__ out, int64_t out_stride, int H, int64_t part_tokens,
-        const float* __restrict__ sinks, const bf16* __restrict__ gate, int64_t gate_stride) {
+        const float* __restrict__ sinks, const bf16* __restrict__ gate, int64_t gate_stride,
+        int gate_per_head) {
     pdl_wait();
     pdl_trigger();
     const int r = row_list ? row_list[blockIdx.x] : blockIdx.x;
@@ -993,9 +1008,9 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) attn_merge_kernel(
             float4 r = make_float4(some ? num.x / den : 0.f, some ? num.y / den : 0.f,
                                    some ? num.z / den : 0.f, some ? num.w / den : 0.f);
             if (gate) {
-                const bf16* gt = gate + (int64_t)t * gate_stride + (int64_t)head * HD + d;
-                r.x *= sigmoid_of(gt[0]); r.y *= sigmoid_of(gt[1]);
-                r.z *= sigmoid_of(gt[2]); r.w *= sigmoid_of(gt[3]);
+                const float2 ga = gate_pair(gate, gate_stride, gate_per_head, t, head, d);
+                const float2 gb = gate_pair(gate, gate_stride, gate_per_head, t, head, d + 2);
+                r.x *= ga.x; r.y *= ga.y; r.z *= gb.x; r.w *= gb.y;
             }
             __nv_bfloat162 lo = __floats2bfloat162_rn(r.x, r.y);
             __nv_bfloat162 hi = __floats2bfloat162_rn(r.z, r.w);
@@ -1054,7 +1069,8 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
                               float scale, int window, int split, int n_splits, float* scratch,
                               int64_t n_tokens_total, const float* slopes, const float* sinks,
                               const void* gate, int64_t gate_stride, int* merge_count,
-                              int planes, float softcap, int chunk, cudaStream_t stream) {
+                              int planes, float softcap, int chunk, int gate_per_head,
+                              cudaStream_t stream) {
     if (n_list <= 0 || max_new <= 0) return 0;
     if (planes < 1 || planes > 2 || chunk < 0 || softcap < 0.f) return (int)cudaErrorInvalidValue;
     if (H <= 0 || G <= 0 || H % G != 0 || page_size <= 0 || window < 0 || n_list > 65535 ||
@@ -1062,8 +1078,10 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
         return (int)cudaErrorInvalidValue;
     if (((uintptr_t)q & 15) || ((uintptr_t)pages & 15) || ((uintptr_t)out & 3))
         return (int)cudaErrorInvalidValue;
-    if (gate && ((gate_stride % 2) != 0 || ((uintptr_t)gate & 3))) return (int)cudaErrorInvalidValue;
+    if (gate && !gate_per_head && ((gate_stride % 2) != 0 || ((uintptr_t)gate & 3)))
+        return (int)cudaErrorInvalidValue;
     AttnArgs a;
+    a.gate_per_head = gate_per_head;
     a.q = (const bf16*)q; a.q_stride = q_stride;
     a.pages = (const bf16*)pages; a.block_table = block_table; a.table_stride = table_stride;
     a.page_size = page_size; a.row_start = row_start; a.row_pos0 = row_pos0; a.row_list = row_list;
@@ -1119,7 +1137,7 @@ SLLM_EXPORT int sllm_attn_mma(const void* q, int64_t q_stride, const void* pages
         e = sllm_launch_pdl(attn_merge_kernel, mgrid, dim3(MERGE_WARPS * 32), 0, stream,
                             (const float*)a.part_o, (const float*)a.part_lse, n_splits, row_start,
                             row_list, (bf16*)out, out_stride, H, a.part_tokens, a.sinks, a.gate,
-                            a.gate_stride);
+                            a.gate_stride, a.gate_per_head);
         if (e != cudaSuccess) return (int)e;
     }
     return 0;
@@ -1186,7 +1204,7 @@ SLLM_EXPORT int sllm_attn_mma_decode_biased(const void* qkv, int64_t qkv_stride,
         e = sllm_launch_pdl(attn_merge_kernel, mgrid, dim3(MERGE_WARPS * 32), 0, stream,
                             (const float*)a.part_o, (const float*)a.part_lse, n_splits, row_start,
                             row_list, (bf16*)out, out_stride, H, a.part_tokens, a.sinks, a.gate,
-                            a.gate_stride);
+                            a.gate_stride, a.gate_per_head);
         if (e != cudaSuccess) return (int)e;
     }
     return 0;
@@ -1313,7 +1331,7 @@ SLLM_EXPORT int sllm_attn_mma_split_noalloc(const void* q, int64_t q_stride, con
         dim3 mgrid(n_list, (H + MERGE_WARPS - 1) / MERGE_WARPS);
         attn_merge_kernel<<<mgrid, MERGE_WARPS * 32, 0, stream>>>(
             a.part_o, a.part_lse, n_splits, row_start, row_list, (bf16*)out, out_stride, H,
-            a.part_tokens, (const float*)nullptr, (const bf16*)nullptr, (int64_t)0);
+            a.part_tokens, (const float*)nullptr, (const bf16*)nullptr, (int64_t)0, 0);
         SLLM_LAUNCH_CHECK();
     }
     return 0;

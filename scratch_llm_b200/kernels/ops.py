@@ -644,10 +644,13 @@ def attention_mma(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tenso
     finishes last for a row, kv head and tile of 16 query heads merges the splits, no merge kernel follows (launches
     share the counters per device and must be ordered by their stream)."""
     _head_vectors(slopes, sinks, n_heads)
+    gate_per_head = False
     if gate is not None:
         _need(gate, torch.bfloat16, "gate", contiguous=False)
-        if gate.shape != q.shape or gate.stride(1) != 1:
-            raise KernelError("gate must have the queries' shape and contiguous rows")
+        gate_per_head = gate.shape == (q.shape[0], n_heads) and head_dim != 1
+        if (gate.shape != q.shape and not gate_per_head) or gate.stride(1) != 1:
+            raise KernelError("gate must have the queries' shape, or one column per head, and "
+                              "contiguous rows")
     _need(q, torch.bfloat16, "q", contiguous=False)
     _need(pages, torch.bfloat16, "pages")
     _need(out, torch.bfloat16, "out", contiguous=False)
@@ -683,8 +686,8 @@ def attention_mma(q: torch.Tensor, pages: torch.Tensor, block_table: torch.Tenso
         c_int(n_heads), c_int(n_kv_heads), c_float(scale), c_int(window or 0),
         c_int(int(split)), c_int(n_splits), _ptr(scratch), c_int64(n_tokens), _ptr(slopes),
         _ptr(sinks), _ptr(gate), c_int64(gate.stride(0) if gate is not None else 0),
-        _ptr(counters), c_int(planes), c_float(softcap), c_int(chunk or 0), _stream()),
-        "attention_mma")
+        _ptr(counters), c_int(planes), c_float(softcap), c_int(chunk or 0),
+        c_int(int(gate_per_head)), _stream()), "attention_mma")
     return out
 
 

@@ -187,24 +187,29 @@ class NormedAttention(Mixer):
             # (padding tokens get no attention output: zeros, so that what follows stays finite)
             out = (torch.zeros if batch.padded else torch.empty)(
                 (proj.shape[0], H * hd), dtype=proj.dtype, device=proj.device)
+        g0 = (H + (0 if self.borrow_kv else 2 * G)) * hd
+        gate = proj[:, g0:g0 + H] if self.has_gate else None
         if self._tensor_cores(proj.dtype):
-            self._attend_tensor_cores(q, out, batch, cache)
+            # (the gate in the kernels' epilogues, where they have one)
+            if self._attend_tensor_cores(q, out, batch, cache, gate):
+                gate = None
         else:
             ops.attention_simt(q, cache.pages, cache.block_table, cache.page_size,
                                batch.row_start, batch.row_pos0, out, batch.n_rows, batch.max_new,
                                H, G, hd, self.scale, self.window, None, self.sinks,
                                softcap=self.softcap, chunk=self.chunk)
-        if self.has_gate:
-            g0 = (H + (0 if self.borrow_kv else 2 * G)) * hd
-            ops.head_gate(out, proj[:, g0:g0 + H], H)
+        if gate is not None:
+            ops.head_gate(out, gate, H)
         return out
 
-    def _attend_tensor_cores(self, q, out, batch, cache: CacheView) -> None:
+    def _attend_tensor_cores(self, q, out, batch, cache: CacheView, gate) -> bool:
         """Rows with several new tokens go to the tcgen05 kernel where the longest of them fills
         one of its query tiles, else to the wide ``mma.sync`` kernel; rows with one token to the
         split kernel (as :class:`~.attention.GQAttention` does).  All take the cap, the chunks
-        and the sink."""
+        and the sink.  Returns whether the gate was applied (the tcgen05 kernel has none: a step
+        that uses it gates all of its rows afterwards)."""
         H, G, hd = self.n_heads, self.n_kv_heads, self.head_dim
+        gated = True
         common = (q, cache.pages, cache.block_table, cache.page_size, batch.row_start,
                   batch.row_pos0, out)
         if batch.n_multi and batch.max_new_multi * (H // G) >= TC_MIN_PACKED_QUERIES and \
@@ -214,10 +219,11 @@ class NormedAttention(Mixer):
             ops.attention_tc(*common, batch.multi_rows, batch.n_multi, batch.max_new_multi, H, G,
                              hd, self.scale, self.window, None, self.sinks, biased=True,
                              softcap=self.softcap, chunk=self.chunk)
+            gated, gate = False, None
         elif batch.n_multi:
             ops.attention_mma(*common, batch.multi_rows, batch.n_multi, batch.max_new_multi, H, G,
                               hd, self.scale, self.window, split=False, sinks=self.sinks,
-                              softcap=self.softcap, chunk=self.chunk)
+                              softcap=self.softcap, chunk=self.chunk, gate=gate)
         if batch.n_single:
             reach = self.window or self.chunk
             context = batch.context_bucket if reach is None \
@@ -231,8 +237,9 @@ class NormedAttention(Mixer):
             ctas = batch.n_single * G * (-(-(H // G) // 16)) * n_splits
             ops.attention_mma(*common, batch.single_rows, batch.n_single, 1, H, G, hd, self.scale,
                               self.window, split=True, n_splits=n_splits, scratch=scratch,
-                              sinks=self.sinks, softcap=self.softcap, chunk=self.chunk,
+                              sinks=self.sinks, softcap=self.softcap, chunk=self.chunk, gate=gate,
                               merge_inside=ctas <= ops.attention_decode_slots(hd))
+        return gated
 
     # -- for a block that multiplies several branches' activations by one joined output matrix
 

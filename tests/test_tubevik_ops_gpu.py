@@ -210,9 +210,11 @@ def run_attention(kind, q, pages, table, page_size, pos0, H, G, hd, scale, n_spl
         if n_splits > 1:
             scratch = torch.empty(o.attention_mma_scratch_floats(n, H, hd, n_splits),
                                   dtype=torch.float32, device=DEV)
+        gate = kw.pop("gate", None)
         o.attention_mma(qd, pages, table, page_size, row_start, row_pos0, out, i32([0]), 1, n, H,
                         G, hd, scale, window, split=(kind == "split"), n_splits=n_splits,
-                        scratch=scratch, sinks=sinks, **kw)
+                        scratch=scratch, sinks=sinks,
+                        gate=None if gate is None else gate.to(DEV, dtype), **kw)
     return out.float().cpu().view(n, H, hd)
 
 
@@ -261,6 +263,13 @@ def test_attention_with_chunks_cap_and_zero_sink(kind, dtype, hd, n_new, n_split
         got = run_attention(kind, q, pages, table, page_size, pos0, H, G, hd, scale, n_splits,
                             softcap=cap, zero_sink=sink, **kw)
         torch.testing.assert_close(got, want, **tol)
+    if kind in ("wide", "split"):
+        # one gate per token and head in the kernel's epilogue, and where the last CTA merges
+        gate = rnd(g, (n_new, H), 2.0, dtype)
+        for inside in (False, True):
+            got = run_attention(kind, q, pages, table, page_size, pos0, H, G, hd, scale, n_splits,
+                                softcap=2.5, zero_sink=True, gate=gate, merge_inside=inside, **kw)
+            torch.testing.assert_close(got, want * torch.sigmoid(gate)[:, :, None], **tol)
     if first_seen == 0:
         return
     # one token more in the mask would show
