@@ -145,6 +145,20 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+# Optional, for mixers and feed-forwards that END with a matrix product into the stream and sit
+# in a block that joins its branches' output matrices into one product
+# (:class:`scratch_llm_b200.parts.block.SharedNormBlock`):
+#
+#   out_segments() -> [(W [hidden, width], weight in the layer's sum), ...] | None   (after load)
+#   activations_into(x, [batch, cache, write, position,] outs)   what each W multiplies, written
+#       into the given column slices [N, width] of the block's buffer (a mixer takes the step's
+#       arguments, a feed-forward x alone); in padded steps the slices hold zeros beforehand
+#   release_out()   the part's own output matrices are no longer needed
+#
+# A mixer may also RETURN a weighted sum of tensors from forward()
+# (:class:`scratch_llm_b200.parts.stream.Terms`) to a block and a norm that take one.
+
+
 class TokenMix(Part):
     """Something that mixes a token's input with the previous token's before a mixer reads it
     (a token shift).  It states the state it carries (``state_spec()``) and offers what a norm
