@@ -36,9 +36,11 @@ struct NormRopeArgs {
     int H; int G; int hd; int has_kv; int write;
 };
 
-template <typename T>
+// VECTOR: the token's columns come and go 16 bytes at a time (hd a multiple of 16 / sizeof(T),
+// rows and bases 16-byte aligned); the arithmetic in between is the same.
+template <typename T, bool VECTOR>
 __global__ void __launch_bounds__(NR_THREADS) norm_rope_kv_write_kernel(const NormRopeArgs a) {
-    extern __shared__ float s[];        // the token's q (and k, v) columns
+    extern __shared__ __align__(16) float s[];        // the token's q (and k, v) columns
     __shared__ float scratch[33];
     pdl_wait();
     pdl_trigger();
@@ -51,8 +53,18 @@ __global__ void __launch_bounds__(NR_THREADS) norm_rope_kv_write_kernel(const No
     const int q_cols = a.H * hd, k_cols = kv ? a.G * hd : 0;
     const int cols = q_cols + 2 * k_cols;
     T* x = reinterpret_cast<T*>(a.x) + n * a.ld;
-    for (int c = tid; c < cols; c += NR_THREADS)
-        s[c] = to_float(x[c]) + (a.bias ? a.bias[c] : 0.f);
+    constexpr int VN = Vec<T>::N;
+    if (VECTOR) {
+        for (int c = tid * VN; c < cols; c += NR_THREADS * VN) {
+            float v[VN];
+            Vec<T>::load(x + c, v);
+#pragma unroll
+            for (int i = 0; i < VN; ++i) s[c + i] = v[i] + (a.bias ? a.bias[c + i] : 0.f);
+        }
+    } else {
+        for (int c = tid; c < cols; c += NR_THREADS)
+            s[c] = to_float(x[c]) + (a.bias ? a.bias[c] : 0.f);
+    }
     __syncthreads();
     if (a.q_gain) {     // one factor for all of q, one for all of k
         float sq = 0.f, sk = 0.f;
@@ -93,7 +105,11 @@ __global__ void __launch_bounds__(NR_THREADS) norm_rope_kv_write_kernel(const No
         }
         __syncthreads();
     }
-    for (int c = tid; c < q_cols; c += NR_THREADS) x[c] = from_float<T>(s[c]);
+    if (VECTOR) {
+        for (int c = tid * VN; c < q_cols; c += NR_THREADS * VN) Vec<T>::store(x + c, s + c);
+    } else {
+        for (int c = tid; c < q_cols; c += NR_THREADS) x[c] = from_float<T>(s[c]);
+    }
     if (!kv) return;
     const int pos = a.positions[n];
     const int page = a.block_table[(int64_t)row * a.table_stride + pos / a.page_size];
@@ -101,11 +117,20 @@ __global__ void __launch_bounds__(NR_THREADS) norm_rope_kv_write_kernel(const No
     T* pages = reinterpret_cast<T*>(a.pages);
     const int64_t plane = (int64_t)a.G * a.page_size * hd;
     T* k_dst = pages + (int64_t)page * 2 * plane + (int64_t)(pos % a.page_size) * hd;
-    for (int c = tid; c < k_cols; c += NR_THREADS) {
-        const int g = c / hd, d = c - g * hd;
-        const int64_t off = (int64_t)g * a.page_size * hd + d;
-        k_dst[off] = from_float<T>(s[q_cols + c]);
-        k_dst[plane + off] = from_float<T>(s[q_cols + k_cols + c]);
+    if (VECTOR) {
+        for (int c = tid * VN; c < k_cols; c += NR_THREADS * VN) {
+            const int g = c / hd, d = c - g * hd;
+            const int64_t off = (int64_t)g * a.page_size * hd + d;
+            Vec<T>::store(k_dst + off, s + q_cols + c);
+            Vec<T>::store(k_dst + plane + off, s + q_cols + k_cols + c);
+        }
+    } else {
+        for (int c = tid; c < k_cols; c += NR_THREADS) {
+            const int g = c / hd, d = c - g * hd;
+            const int64_t off = (int64_t)g * a.page_size * hd + d;
+            k_dst[off] = from_float<T>(s[q_cols + c]);
+            k_dst[plane + off] = from_float<T>(s[q_cols + k_cols + c]);
+        }
     }
 }
 
@@ -138,25 +163,25 @@ SLLM_EXPORT int sllm_norm_rope_kv_write(void* x, int64_t ld, const int* position
     a.page_size = page_size; a.H = H; a.G = G; a.hd = hd; a.has_kv = has_kv; a.write = write;
     const size_t smem = (size_t)(H + (has_kv ? 2 * G : 0)) * hd * sizeof(float);
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
-    cudaError_t e;
+    if (dtype != 0 && dtype != 1) return (int)cudaErrorInvalidValue;
+    const int vn = dtype == 0 ? 4 : 8;
+    const bool vector = hd % vn == 0 && ld % vn == 0 && !(((uintptr_t)x | (uintptr_t)pages) & 15);
+    cudaError_t e = cudaSuccess;
+#define SLLM_NR_LAUNCH(T, V)                                                                   \
+    do {                                                                                       \
+        if (smem > 48 * 1024) {                                                                \
+            e = cudaFuncSetAttribute(norm_rope_kv_write_kernel<T, V>,                          \
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+            if (e != cudaSuccess) return (int)e;                                               \
+        }                                                                                      \
+        e = sllm_launch_pdl(norm_rope_kv_write_kernel<T, V>, dim3(n_tokens), dim3(NR_THREADS), \
+                            smem, stream, a);                                                  \
+    } while (0)
     if (dtype == 0) {
-        if (smem > 48 * 1024) {
-            e = cudaFuncSetAttribute(norm_rope_kv_write_kernel<float>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return (int)e;
-        }
-        e = sllm_launch_pdl(norm_rope_kv_write_kernel<float>, dim3(n_tokens), dim3(NR_THREADS),
-                            smem, stream, a);
-    } else if (dtype == 1) {
-        if (smem > 48 * 1024) {
-            e = cudaFuncSetAttribute(norm_rope_kv_write_kernel<__nv_bfloat16>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return (int)e;
-        }
-        e = sllm_launch_pdl(norm_rope_kv_write_kernel<__nv_bfloat16>, dim3(n_tokens),
-                            dim3(NR_THREADS), smem, stream, a);
+        if (vector) SLLM_NR_LAUNCH(float, true); else SLLM_NR_LAUNCH(float, false);
     } else {
-        return (int)cudaErrorInvalidValue;
+        if (vector) SLLM_NR_LAUNCH(__nv_bfloat16, true); else SLLM_NR_LAUNCH(__nv_bfloat16, false);
     }
+#undef SLLM_NR_LAUNCH
     return (int)e;
 }
